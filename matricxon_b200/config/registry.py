@@ -48,11 +48,12 @@ def resolve_architecture(raw: dict[str, Any]) -> ArchitectureEntry:
     architectures = raw.get("architectures")
     if isinstance(architectures, list):
         names.extend(str(a) for a in architectures)
-    if isinstance(raw.get("model_type"), str):
-        names.append(raw["model_type"])
+    for key in ("architecture", "model_type"):
+        if isinstance(raw.get(key), str):
+            names.append(raw[key])
     if not names:
         raise UnsupportedArchitectureError(
-            "config.json has neither 'architectures' nor 'model_type'; cannot choose a model")
+            "config.json has none of 'architectures', 'architecture' and 'model_type'; cannot choose a model")
     for name in names:
         if name in _REGISTRY:
             return _REGISTRY[name]
@@ -90,6 +91,14 @@ def _register_builtin() -> None:
         name="starcoder2",
         aliases=("Starcoder2ForCausalLM",),
         config_class=Starcoder2Config,
+        build_model=_build_decoder,
+    ))
+    from matricxon_b200.config.busatar import BusatarConfig
+
+    register_architecture(ArchitectureEntry(
+        name="Busatar",
+        aliases=("busatar",),
+        config_class=BusatarConfig,
         build_model=_build_decoder,
     ))
 

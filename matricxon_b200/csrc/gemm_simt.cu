@@ -20,7 +20,13 @@ template <typename TIn, typename TOut>
 __global__ void __launch_bounds__(THREADS)
 gemm_simt_kernel(const TIn* __restrict__ A, const TIn* __restrict__ W,
                  const float* __restrict__ bias, const float* residual, TOut* out,
-                 int M, int N, int K, int lda, int ldw, int ldo, int mode) {
+                 int M, int N, int K, int lda, int ldw, int ldo, int mode,
+                 long long a_batch, long long w_batch, long long o_batch, long long bias_batch) {
+    // blockIdx.z: one of several independent products (a head, a block of a block-diagonal matrix)
+    A += (size_t)blockIdx.z * a_batch;
+    W += (size_t)blockIdx.z * w_batch;
+    out += (size_t)blockIdx.z * o_batch;
+    if (bias) bias += (size_t)blockIdx.z * bias_batch;
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -93,11 +99,35 @@ extern "C" int mx_gemm_simt(const void* A, const void* W, int in_dtype, const fl
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (grid.y > 65535) MX_REFUSE("gemm: M = %d is beyond this kernel's grid", M);
 #define MX_GEMM(TI, TO) \
-    gemm_simt_kernel<TI, TO><<<grid, THREADS, 0, stream>>>((const TI*)A, (const TI*)W, bias, residual, (TO*)out, M, N, K, lda, ldw, ldo, mode)
+    gemm_simt_kernel<TI, TO><<<grid, THREADS, 0, stream>>>((const TI*)A, (const TI*)W, bias, residual, (TO*)out, M, N, K, lda, ldw, ldo, mode, 0, 0, 0, 0)
     if (in_dtype == MX_DTYPE_F32 && out_dtype == MX_DTYPE_F32) MX_GEMM(float, float);
     else if (in_dtype == MX_DTYPE_BF16 && out_dtype == MX_DTYPE_F32) MX_GEMM(__nv_bfloat16, float);
     else if (in_dtype == MX_DTYPE_BF16 && out_dtype == MX_DTYPE_BF16) MX_GEMM(__nv_bfloat16, __nv_bfloat16);
     else MX_REFUSE("gemm: float inputs with a bfloat16 output are not used by any path");
+#undef MX_GEMM
+    return mx_launch_status();
+}
+
+// `batch` independent products of the same shape in one launch: product b reads A + b * a_batch
+// (rows lda apart) and W + b * w_batch, adds bias + b * bias_batch and writes out + b * o_batch (rows
+// ldo apart). The operands of a batch may interleave (heads side by side in one row). mode 0 writes
+// the input dtype, mode 3 float.
+extern "C" int mx_gemm_batched_simt(const void* A, const void* W, int in_dtype, const float* bias, void* out,
+                                    int out_dtype, int M, int N, int K, int lda, int ldw, int ldo, int batch,
+                                    long long a_batch, long long w_batch, long long o_batch,
+                                    long long bias_batch, int mode, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || batch <= 0) return MX_OK;
+    if (K <= 0) MX_REFUSE("batched gemm: K must be positive, got %d", K);
+    if (mode != 0 && mode != 3) MX_REFUSE("batched gemm: epilogue mode %d", mode);
+    const int expected_out = (mode == 3 || in_dtype == MX_DTYPE_F32) ? MX_DTYPE_F32 : MX_DTYPE_BF16;
+    if (out_dtype != expected_out) MX_REFUSE("batched gemm: mode %d writes dtype %d, not %d", mode, expected_out, out_dtype);
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
+    if (grid.y > 65535 || batch > 65535) MX_REFUSE("batched gemm: M = %d, batch = %d is beyond this kernel's grid", M, batch);
+#define MX_GEMM(TI, TO) \
+    gemm_simt_kernel<TI, TO><<<grid, THREADS, 0, stream>>>((const TI*)A, (const TI*)W, bias, nullptr, (TO*)out, M, N, K, lda, ldw, ldo, mode, a_batch, w_batch, o_batch, bias_batch)
+    if (in_dtype == MX_DTYPE_F32) MX_GEMM(float, float);
+    else if (out_dtype == MX_DTYPE_F32) MX_GEMM(__nv_bfloat16, float);
+    else MX_GEMM(__nv_bfloat16, __nv_bfloat16);
 #undef MX_GEMM
     return mx_launch_status();
 }

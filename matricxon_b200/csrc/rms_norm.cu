@@ -1,0 +1,107 @@
+// RMS norm over rows of the float residual stream, and the post-norm step that forms its own input.
+//
+//   unit(x) = x / sqrt(mean(x^2) + eps)          (eps inside the root)
+//   mx_rmsnorm:      out[r] = unit(x[rows ? rows[r] : r]) * (offset + weight)
+//   mx_rmsnorm_sum:  x[r]  <- unit(alpha * x[r] + acc[r]) * (offset + weight)   (in place, float)
+//                    act[r] <- the same row rounded to the activation dtype (optional)
+//
+// `offset` is 1 for checkpoints that store the scale as its distance from one and 0 for a plain
+// scale. The second form is a post-norm sublayer's end: `acc` is the float result of the sublayer's
+// last product, `alpha` the weight of the skip path; the next sublayer reads `act` (a bfloat16 copy
+// when serving; on the 32-bit path it reads x itself and act is null).
+//
+// One block per row; sums of squares are float and their order depends on the thread layout alone,
+// so a row's result does not depend on the other rows of the step.
+// mx_cast_rows rounds a float matrix to the activation dtype (the first sublayer's input).
+#include "common.cuh"
+
+namespace {
+
+constexpr int RMS_MAX_PER_THREAD = 16;   // row values a thread keeps in registers
+
+template <typename TOut>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                               const float* __restrict__ weight, float offset, TOut* __restrict__ out,
+                               int hidden, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * hidden;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = xr[i];
+        s = fmaf(v, v, s);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(s, scratch) / (float)hidden + eps);
+    TOut* o = out + (size_t)r * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+        o[i] = from_float<TOut>(xr[i] * inv * (offset + weight[i]));
+}
+
+template <typename TAct>
+__global__ void rmsnorm_sum_kernel(float* x, const float* __restrict__ acc, float alpha,
+                                   const float* __restrict__ weight, float offset, TAct* act,
+                                   int hidden, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    float* xr = x + (size_t)r * hidden;
+    const float* ar = acc + (size_t)r * hidden;
+    float kept[RMS_MAX_PER_THREAD];
+    float s = 0.f;
+    int n = 0;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x, ++n) {
+        const float v = fmaf(alpha, xr[i], ar[i]);
+        if (n < RMS_MAX_PER_THREAD) kept[n] = v; else xr[i] = v;      // long rows park the sum in x itself
+        s = fmaf(v, v, s);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(s, scratch) / (float)hidden + eps);
+    n = 0;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x, ++n) {
+        const float v = (n < RMS_MAX_PER_THREAD ? kept[n] : xr[i]) * inv * (offset + weight[i]);
+        xr[i] = v;
+        if (act) act[(size_t)r * hidden + i] = from_float<TAct>(v);
+    }
+}
+
+__global__ void cast_rows_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ out, long long count) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) out[i] = __float2bfloat16_rn(x[i]);
+}
+
+int threads_for(int hidden) { return hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128); }
+
+}  // namespace
+
+extern "C" int mx_rmsnorm(const float* x, const int* rows, const float* weight, float offset, void* out,
+                          int out_dtype, int n_rows, int hidden, float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return MX_OK;
+    if (hidden <= 0) MX_REFUSE("rmsnorm: hidden must be positive, got %d", hidden);
+    const int threads = threads_for(hidden);
+    if (out_dtype == MX_DTYPE_F32)
+        rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, rows, weight, offset, (float*)out, hidden, eps);
+    else
+        rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(x, rows, weight, offset,
+                                                                     (__nv_bfloat16*)out, hidden, eps);
+    return mx_launch_status();
+}
+
+extern "C" int mx_rmsnorm_sum(float* x, const float* acc, float alpha, const float* weight, float offset,
+                              void* act, int act_dtype, int n_rows, int hidden, float eps,
+                              cudaStream_t stream) {
+    if (n_rows <= 0) return MX_OK;
+    if (hidden <= 0) MX_REFUSE("rmsnorm: hidden must be positive, got %d", hidden);
+    if (acc == nullptr) MX_REFUSE("rmsnorm with sum: no accumulator");
+    const int threads = threads_for(hidden);
+    if (act == nullptr || act_dtype == MX_DTYPE_F32)
+        rmsnorm_sum_kernel<float><<<n_rows, threads, 0, stream>>>(x, acc, alpha, weight, offset, (float*)act,
+                                                                 hidden, eps);
+    else
+        rmsnorm_sum_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(x, acc, alpha, weight, offset,
+                                                                         (__nv_bfloat16*)act, hidden, eps);
+    return mx_launch_status();
+}
+
+extern "C" int mx_cast_rows(const float* x, void* out, long long count, cudaStream_t stream) {
+    if (count <= 0) return MX_OK;
+    cast_rows_kernel<<<(unsigned)((count + 255) / 256), 256, 0, stream>>>(x, (__nv_bfloat16*)out, count);
+    return mx_launch_status();
+}

@@ -59,15 +59,13 @@ class CachePlan:
 
 def model_weight_specs(spec: ModelSpec) -> list[WeightSpec]:
     """Every tensor the model expects, by name, without building anything."""
-    specs = [WeightSpec(f"{spec.embedding_name}.weight", (spec.vocab_size, spec.hidden_size),
+    specs = [WeightSpec(f"{spec.embedding_name}{spec.weight_suffix}", (spec.vocab_size, spec.hidden_size),
                         role="matrix", init="weight")]
     for index, layer in enumerate(spec.layers):
-        prefix = f"{spec.layer_prefix}.{index}."
-        specs.extend(part_class("block", layer.block).weight_specs(layer, prefix))
-    specs.extend(part_class("norm", spec.final_norm.kind).weight_specs(
-        spec.final_norm, f"{spec.final_norm_name}."))
+        specs.extend(part_class("block", layer.block).weight_specs(layer, spec.layer_prefix_of(index)))
+    specs.extend(part_class("norm", spec.final_norm.kind).weight_specs(spec.final_norm, spec.norm_prefix))
     if not spec.tie_word_embeddings:
-        specs.append(WeightSpec(f"{spec.head_name}.weight", (spec.vocab_size, spec.hidden_size),
+        specs.append(WeightSpec(f"{spec.head_name}{spec.weight_suffix}", (spec.vocab_size, spec.hidden_size),
                                 role="matrix", init="weight"))
     if spec.head_bias:
         specs.append(WeightSpec(f"{spec.head_name}.bias", (spec.vocab_size,), role="vector", init="bias"))
@@ -118,9 +116,9 @@ class DecoderModel:
     def __init__(self, spec: ModelSpec, runtime: Runtime) -> None:
         self.spec = spec
         self.runtime = runtime
-        self.layers = [part_class("block", layer.block)(layer, runtime, f"{spec.layer_prefix}.{index}.")
+        self.layers = [part_class("block", layer.block)(layer, runtime, spec.layer_prefix_of(index))
                        for index, layer in enumerate(spec.layers)]
-        self.final_norm = build_part("norm", spec.final_norm, runtime, f"{spec.final_norm_name}.")
+        self.final_norm = build_part("norm", spec.final_norm, runtime, spec.norm_prefix)
         # decode steps may be captured as CUDA graphs only if every part is stream-ordered
         self.capturable = self.final_norm.capturable and all(layer.capturable for layer in self.layers)
         self.cache_plan = plan_cache(spec)
@@ -133,12 +131,12 @@ class DecoderModel:
         return model_weight_specs(self.spec)
 
     def load(self, fetch) -> None:
-        self.embedding = fetch(f"{self.spec.embedding_name}.weight")
+        self.embedding = fetch(f"{self.spec.embedding_name}{self.spec.weight_suffix}")
         for layer in self.layers:
             layer.load(fetch)
         self.final_norm.load(fetch)
         self.head = (self.embedding if self.spec.tie_word_embeddings
-                     else fetch(f"{self.spec.head_name}.weight"))
+                     else fetch(f"{self.spec.head_name}{self.spec.weight_suffix}"))
         self.head_bias = fetch(f"{self.spec.head_name}.bias") if self.spec.head_bias else None
 
     def bind_cache(self, group_storage: list[torch.Tensor], state_storage: list[torch.Tensor | None]) -> None:
@@ -160,12 +158,15 @@ class DecoderModel:
         kernels.embed(ctx.token_ids, self.embedding, x, ctx.status, self.spec.embedding_scale)
         # a block may hand the next one a residual sum still to be added up (the next norm adds as it reads)
         ctx.pending_sum_wanted = True
+        taps = ctx.memo.get("layer_outputs")
         try:
             for position, entry in enumerate(self.spec.schedule):
                 layer = self.layers[entry.layer]
                 if isinstance(x, PendingSum) and not layer.takes_pending_sum:
                     x = x.tensor()
                 x = layer.forward(x, ctx, self.bindings[position])
+                if taps is not None:        # a caller that wants the stream after every schedule entry
+                    taps.append((x.tensor() if isinstance(x, PendingSum) else x).clone())
         finally:
             ctx.pending_sum_wanted = False
         return x.tensor() if isinstance(x, PendingSum) else x      # the last block's sum, added up here

@@ -503,3 +503,222 @@ def paged_attention_mma(q: torch.Tensor, q_stride: int, cache: torch.Tensor,
 def mma_attention_supported(dtype: torch.dtype, head_dim: int, page_size: int, q_stride: int) -> bool:
     return (dtype == torch.bfloat16 and head_dim in (64, 128) and page_size in (8, 16, 32)
             and q_stride % 8 == 0)
+
+
+# ---------------------------------------------------------------------- RMS norm, post-norm sums
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, offset: float, eps: float, out: torch.Tensor,
+            rows: torch.Tensor | None = None) -> None:
+    """out[r] = x[row] / sqrt(mean(x[row]^2) + eps) * (offset + weight), row = rows[r] if given else r."""
+    _need(x, "x", torch.float32)
+    _need(weight, "weight", torch.float32)
+    _need(out, "out")
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    n_rows, hidden = out.shape
+    assert x.shape[1] == hidden and weight.numel() == hidden
+    assert (rows.numel() if rows is not None else x.shape[0]) == n_rows
+    check(library().mx_rmsnorm(_ptr(x), _ptr(rows), _ptr(weight), float(offset), _ptr(out),
+                               dtype_code(out.dtype), n_rows, hidden, float(eps), _stream()), "rmsnorm")
+    _launched()
+
+
+def rmsnorm_sum(x: torch.Tensor, acc: torch.Tensor, alpha: float, weight: torch.Tensor, offset: float,
+                eps: float, act: torch.Tensor | None = None) -> None:
+    """``x <- unit(alpha * x + acc) * (offset + weight)`` in place (float32); ``act``, when given, gets the
+    same rows in its own dtype."""
+    _need(x, "x", torch.float32)
+    _need(acc, "acc", torch.float32)
+    _need(weight, "weight", torch.float32)
+    assert acc.shape == x.shape and weight.numel() == x.shape[1]
+    if act is not None:
+        _need(act, "act")
+        assert act.shape == x.shape
+    check(library().mx_rmsnorm_sum(_ptr(x), _ptr(acc), float(alpha), _ptr(weight), float(offset), _ptr(act),
+                                   dtype_code(act.dtype) if act is not None else F32, x.shape[0], x.shape[1],
+                                   float(eps), _stream()), "rmsnorm_sum")
+    _launched()
+
+
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out (bfloat16) = x (float32), element by element."""
+    _need(x, "x", torch.float32)
+    _need(out, "out", torch.bfloat16)
+    assert out.numel() == x.numel()
+    check(library().mx_cast_rows(_ptr(x), _ptr(out), x.numel(), _stream()), "cast_rows")
+    _launched()
+
+
+# ---------------------------------------------------------------------- batched products
+def gemm_batched_simt(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor) -> None:
+    """``out[:, b] = a[:, b] @ w[b].T (+ bias[b])`` for every b on the FP32 cores: a [M, B, K] and out
+    [M, B, N] may be views with any row and batch strides (unit stride along K and N), w [B, N, K],
+    bias float32 [B, N]. ``out`` is in the dtype of ``a`` or float32."""
+    _need(a, "a", contiguous=False)
+    _need(w, "w", a.dtype)
+    _need(out, "out", contiguous=False)
+    m, batch, k = a.shape
+    n = w.shape[1]
+    assert tuple(w.shape) == (batch, n, k) and tuple(out.shape) == (m, batch, n), (a.shape, w.shape, out.shape)
+    if a.stride(2) != 1 or out.stride(2) != 1:
+        raise KernelLibraryError("batched operands must have unit stride along their last axis")
+    if out.dtype not in (a.dtype, torch.float32):
+        raise KernelLibraryError(f"a batched product of {a.dtype} writes {a.dtype} or float32, not {out.dtype}")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        assert tuple(bias.shape) == (batch, n)
+    mode = EPILOGUE_F32 if out.dtype == torch.float32 and a.dtype != torch.float32 else EPILOGUE_NONE
+    check(library().mx_gemm_batched_simt(_ptr(a), _ptr(w), dtype_code(a.dtype), _ptr(bias), _ptr(out),
+                                         dtype_code(out.dtype), m, n, k, a.stride(0), w.stride(1), out.stride(0),
+                                         batch, a.stride(1), w.stride(0), out.stride(1), n, mode, _stream()),
+          "gemm_batched_simt")
+    _launched()
+
+
+# ---------------------------------------------------------------------- latent attention
+def latent_prepare(proj: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor, amplitude: float,
+                   latent_weight: torch.Tensor, eps: float, slots: torch.Tensor | None,
+                   cache: torch.Tensor | None, q_plain: torch.Tensor, q_lat: torch.Tensor, n_heads: int,
+                   dim: int, rot: int, rot_dims: int, rank: int, status: torch.Tensor) -> None:
+    """From the float rows ``[heads x (dim | rot) | rank | rot]`` of the fused query / down projection:
+    the plain query parts, the rotated query parts (at offset ``rank`` of each head of ``q_lat``) and the
+    token's cache vector ``[unit(latent) * latent_weight | rotated shared part]`` at ``slots``.
+    ``cache`` is [pages, 1, 1, page_size, rank + rot]; None stores nothing."""
+    _need(proj, "proj", torch.float32)
+    _need(positions, "positions", torch.int32)
+    _need(freq, "freq", torch.float32)
+    _need(latent_weight, "latent_weight", torch.float32)
+    _need(q_plain, "q_plain")
+    _need(q_lat, "q_lat", q_plain.dtype)
+    n = proj.shape[0]
+    assert freq.numel() == rot_dims // 2 and latent_weight.numel() == rank
+    assert tuple(q_plain.shape) == (n, n_heads * dim) and tuple(q_lat.shape) == (n, n_heads, rank + rot)
+    n_pages = page_size = 0
+    if cache is not None:
+        _need(cache, "cache", q_plain.dtype)
+        _need(slots, "slots", torch.int32)
+        assert tuple(cache.shape[1:3]) == (1, 1) and cache.shape[4] == rank + rot, cache.shape
+        n_pages, page_size = cache.shape[0], cache.shape[3]
+    check(library().mx_latent_prepare(_ptr(proj), proj.stride(0), _ptr(positions), _ptr(freq), float(amplitude),
+                                      _ptr(latent_weight), float(eps), _ptr(slots), _ptr(cache), n_pages,
+                                      page_size, _ptr(q_plain), _ptr(q_lat), dtype_code(q_plain.dtype), n,
+                                      n_heads, dim, rot, rot_dims, rank, _ptr(status), _stream()),
+          "latent_prepare")
+    _launched()
+
+
+def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor,
+                     tok_seq: torch.Tensor, positions: torch.Tensor, rank: int, window: int | None,
+                     scale: float, out: torch.Tensor, status: torch.Tensor) -> None:
+    """Attention of ``q_lat`` [tokens, heads, dk] over the one-vector-per-token cache
+    [pages, 1, 1, page_size, dk]; ``out`` [tokens, heads, rank] is the softmax-weighted sum of the first
+    ``rank`` elements of the visible vectors."""
+    _need(q_lat, "q_lat")
+    _need(cache, "cache", q_lat.dtype)
+    _need(out, "out", q_lat.dtype)
+    for name, tensor in (("block_tables", block_tables), ("tok_seq", tok_seq), ("positions", positions),
+                         ("status", status)):
+        _need(tensor, name, torch.int32)
+    n, n_heads, dk = q_lat.shape
+    assert tuple(cache.shape[1:3]) == (1, 1) and cache.shape[4] == dk, cache.shape
+    assert tuple(out.shape) == (n, n_heads, rank)
+    check(library().mx_latent_attention(_ptr(q_lat), _ptr(cache), dtype_code(q_lat.dtype), cache.shape[0],
+                                        cache.shape[3], _ptr(block_tables), block_tables.stride(0),
+                                        _ptr(tok_seq), _ptr(positions), n, n_heads, rank, dk, int(window or 0),
+                                        float(scale), _ptr(out), _ptr(status), _stream()), "latent_attention")
+    _launched()
+
+
+# ---------------------------------------------------------------------- normalised, gated attention
+def qk_norm_kv_write(proj: torch.Tensor, q_weight: torch.Tensor | None, k_weight: torch.Tensor | None,
+                     eps: float, slots: torch.Tensor | None, cache: torch.Tensor | None, q_out: torch.Tensor,
+                     n_heads: int, n_kv_heads: int, dim: int, vdim: int, status: torch.Tensor) -> None:
+    """From the float rows ``[heads x dim | kv heads x dim | kv heads x vdim | ...]`` of a fused projection:
+    per-head RMS-normalised queries to ``q_out`` [tokens, heads * hd] and normalised keys and plain values
+    to ``slots`` of ``cache`` [pages, 2, kv heads, page_size, hd]; hd >= dim, vdim, tails are zero."""
+    _need(proj, "proj", torch.float32)
+    _need(q_out, "q_out")
+    n = proj.shape[0]
+    hd = q_out.shape[1] // n_heads
+    assert tuple(q_out.shape) == (n, n_heads * hd)
+    for weight in (q_weight, k_weight):
+        if weight is not None:
+            _need(weight, "norm weight", torch.float32)
+            assert weight.numel() == dim
+    n_pages = page_size = 0
+    if cache is not None:
+        _need(cache, "cache", q_out.dtype)
+        _need(slots, "slots", torch.int32)
+        assert tuple(cache.shape[1:3]) == (2, n_kv_heads) and cache.shape[4] == hd, cache.shape
+        n_pages, page_size = cache.shape[0], cache.shape[3]
+    check(library().mx_qk_norm_kv_write(_ptr(proj), proj.stride(0), _ptr(q_weight), _ptr(k_weight), float(eps),
+                                        _ptr(slots), _ptr(cache), n_pages, page_size, _ptr(q_out),
+                                        dtype_code(q_out.dtype), n, n_heads, n_kv_heads, dim, vdim, hd,
+                                        _ptr(status), _stream()), "qk_norm_kv_write")
+    _launched()
+
+
+def sigmoid_gate(attn: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, n_heads: int, vdim: int) -> None:
+    """out[t, h * vdim + e] = attn[t, h * hd + e] * sigmoid(gate[t, h * vdim + e]); ``gate`` is a float32
+    view with any row stride."""
+    _need(attn, "attn")
+    _need(gate, "gate", torch.float32, contiguous=False)
+    _need(out, "out", attn.dtype)
+    n = attn.shape[0]
+    hd = attn.shape[1] // n_heads
+    assert tuple(out.shape) == (n, n_heads * vdim) and tuple(gate.shape) == (n, n_heads * vdim)
+    assert gate.stride(1) == 1
+    check(library().mx_sigmoid_gate(_ptr(attn), _ptr(gate), gate.stride(0), _ptr(out), dtype_code(attn.dtype), n,
+                                    n_heads, vdim, hd, _stream()), "sigmoid_gate")
+    _launched()
+
+
+def clamped_glu(gate_up: torch.Tensor, out: torch.Tensor, limit: float, slope: float, shift: float) -> None:
+    """Rows ``[gate | up]`` -> ``min(gate, limit) * sigmoid(slope * min(gate, limit)) * (clamp(up) + shift)``."""
+    _need(gate_up, "gate_up")
+    _need(out, "out", gate_up.dtype)
+    n, ff = out.shape
+    assert tuple(gate_up.shape) == (n, 2 * ff)
+    check(library().mx_clamped_glu(_ptr(gate_up), gate_up.stride(0), _ptr(out), dtype_code(out.dtype), n, ff,
+                                   float(limit), float(slope), float(shift), _stream()), "clamped_glu")
+    _launched()
+
+
+# ---------------------------------------------------------------------- gated linear recurrence
+def causal_conv(xy: torch.Tensor, x_col: int, conv_weight: torch.Tensor, conv_bias: torch.Tensor | None,
+                state: torch.Tensor, tok_seq: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor,
+                u: torch.Tensor, u_act: torch.Tensor | None) -> None:
+    """The per-channel causal convolution of columns ``x_col ..`` of ``xy`` (float32), continuing from the
+    inputs kept in ``state`` [slots, taps, width]; ``u`` float32, ``u_act`` an optional rounded copy."""
+    _need(xy, "xy", torch.float32)
+    _need(conv_weight, "conv_weight", torch.float32)
+    _need(state, "state", torch.float32)
+    _need(u, "u", torch.float32)
+    n, width = u.shape
+    taps = conv_weight.shape[1]
+    assert tuple(conv_weight.shape) == (width, taps) and tuple(state.shape[1:]) == (taps, width)
+    if u_act is not None:
+        _need(u_act, "u_act")
+        assert u_act.shape == u.shape
+    check(library().mx_causal_conv(_ptr(xy), xy.stride(0), x_col, _ptr(conv_weight), _ptr(conv_bias), _ptr(state),
+                                   _ptr(tok_seq), _ptr(cu_q), _ptr(state_slots), _ptr(u), _ptr(u_act),
+                                   dtype_code(u_act.dtype) if u_act is not None else F32, n, width, taps,
+                                   _stream()), "causal_conv")
+    _launched()
+
+
+def rglru_scan(xy: torch.Tensor, x_col: int, y_col: int, u: torch.Tensor, gates: torch.Tensor,
+               lam: torch.Tensor, decay: float, state: torch.Tensor, cu_q: torch.Tensor,
+               state_slots: torch.Tensor, n_seqs: int, block_width: int, out: torch.Tensor) -> None:
+    """The gated recurrence over every sequence's tokens in order, from and to ``state``; ``gates`` is
+    float32 [tokens, blocks, 2 * block_width] (recurrence gate, then input gate, before their sigmoids)."""
+    for name, tensor in (("xy", xy), ("u", u), ("gates", gates), ("lambda", lam), ("state", state)):
+        _need(tensor, name, torch.float32)
+    _need(out, "out")
+    n, width = u.shape
+    taps = state.shape[1]
+    assert gates.numel() == n * 2 * width and tuple(out.shape) == (n, width) and lam.numel() == width
+    check(library().mx_rglru_scan(_ptr(xy), xy.stride(0), x_col, y_col, _ptr(u), _ptr(gates), _ptr(lam),
+                                  float(decay), _ptr(state), _ptr(cu_q), _ptr(state_slots), _ptr(out),
+                                  dtype_code(out.dtype), n_seqs, width, block_width, taps, _stream()),
+          "rglru_scan")
+    _launched()

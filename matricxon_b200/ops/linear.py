@@ -183,5 +183,15 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, mod
     return out
 
 
-__all__ = ["linear", "chosen_backend", "PendingSum", "resolve_backend", "EPILOGUE_NONE", "EPILOGUE_GELU", "EPILOGUE_RESIDUAL",
+def batched_linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor) -> torch.Tensor:
+    """``out[:, b] = x[:, b] @ weight[b].T (+ bias[b])``: one small product per head of an attention layer or
+    per block of a block-diagonal matrix. x [M, B, K] and out [M, B, N] may be strided views (heads side by
+    side in a row); weight [B, N, K] in the dtype of x; bias float32 [B, N]; out in the dtype of x or float32."""
+    if x.shape[0] == 0:
+        return out
+    kernels.gemm_batched_simt(x, weight, bias, out)
+    return out
+
+
+__all__ = ["linear", "batched_linear", "chosen_backend", "PendingSum", "resolve_backend", "EPILOGUE_NONE", "EPILOGUE_GELU", "EPILOGUE_RESIDUAL",
            "EPILOGUE_F32"]

@@ -1,6 +1,7 @@
 """Parts a model is assembled from. Importing this package registers the built-in kinds."""
 
-from matricxon_b200.parts import attention, block, mlp, norm, rotary  # noqa: F401  (registration)
+from matricxon_b200.parts import (  # noqa: F401  (registration)
+    attention, block, latent_attention, mlp, norm, recurrent, rotary)
 from matricxon_b200.parts.base import (
     Block,
     CacheBinding,

@@ -23,7 +23,7 @@ import os
 import torch
 
 from matricxon_b200.ops import kernels
-from matricxon_b200.ops.linear import EPILOGUE_NONE, EPILOGUE_RESIDUAL, chosen_backend, linear
+from matricxon_b200.ops.linear import EPILOGUE_F32, EPILOGUE_NONE, EPILOGUE_RESIDUAL, chosen_backend, linear
 from matricxon_b200.parts.base import KVCacheRequest, Mixer, build_part, register_part
 from matricxon_b200.parts.rotary import store_without_rotation
 from matricxon_b200.weights.loader import WeightSpec
@@ -99,6 +99,50 @@ def simt_splits(ctx, n_heads: int, n_kv_heads: int, head_dim: int, window: int |
     return n_splits, ctx.scratch(kernels.attention_scratch_bytes(ctx.n_tokens, n_heads, head_dim, n_splits))
 
 
+def paged_attend(q, q_stride, ctx, binding, rt, n_heads, n_kv_heads, head_dim, window, scale):
+    """Attention of the step's query rows (``q``: query head h of a row at column ``h * head_dim``, rows
+    ``q_stride`` apart) over the keys and values already stored in ``binding.kv``: picks the kernel, the
+    tiles and the key splits for this step. Returns [tokens, heads * head_dim] in the runtime dtype."""
+    group = ctx.groups[binding.group]
+    attn = torch.empty((ctx.n_tokens, n_heads * head_dim), dtype=rt.dtype, device=q.device)
+    if kernels.mma_attention_supported(rt.dtype, head_dim, rt.page_size, q_stride):
+        group_size = n_heads // n_kv_heads
+        # prompt portions on tcgen05 when the kernel takes the geometry, else on mma.sync
+        on_tc = _TC_ATTENTION and kernels.tc_attention_supported(rt.dtype, head_dim, rt.page_size,
+                                                                 q_stride, group_size)
+        narrow, n_narrow, wide, n_wide = attention_tiles(ctx, group_size, token_tiles=on_tc)
+        for tiles, n_tiles, is_narrow in ((narrow, n_narrow, True), (wide, n_wide, False)):
+            if n_tiles == 0:
+                continue
+            if on_tc and not is_narrow:
+                n_splits, scratch = tc_tile_splits(ctx, n_tiles, n_narrow == 0, n_heads,
+                                                       n_kv_heads, head_dim, window)
+                kernels.paged_attention_tc(q, q_stride, binding.kv, group.block_tables, ctx.cu_q,
+                                           ctx.context_lens, tiles, n_tiles, ctx.n_tokens,
+                                           n_heads, n_kv_heads, head_dim,
+                                           window, scale, attn, ctx.status,
+                                           n_splits=n_splits, scratch=scratch)
+                continue
+            alone = (n_wide == 0) if is_narrow else (n_narrow == 0)
+            if is_narrow and ctx.padded:
+                tiles, n_tiles = None, ctx.n_seqs      # a batch of decoding requests: tile i is sequence i
+            n_splits, scratch = mma_tile_splits(ctx, n_tiles, is_narrow, alone, n_heads,
+                                                n_kv_heads, head_dim, window)
+            kernels.paged_attention_mma(q, q_stride, binding.kv, group.block_tables,
+                                        ctx.cu_q, ctx.context_lens, tiles, n_tiles, is_narrow,
+                                        ctx.n_tokens, n_heads, n_kv_heads,
+                                        head_dim, window, scale, attn, ctx.status,
+                                        n_splits=n_splits, scratch=scratch)
+    else:
+        n_splits, scratch = simt_splits(ctx, n_heads, n_kv_heads,
+                                                 head_dim, window)
+        kernels.paged_attention(q, q_stride, binding.kv, group.block_tables, ctx.tok_seq,
+                                ctx.positions, ctx.n_tokens, n_heads, n_kv_heads,
+                                head_dim, window, scale, attn, ctx.status,
+                                n_splits=n_splits, scratch=scratch)
+    return attn
+
+
 @register_part("mixer", "attention")
 class PagedAttention(Mixer):
     def __init__(self, spec, runtime, prefix):
@@ -170,42 +214,84 @@ class PagedAttention(Mixer):
             qkv = linear(h, self.qkv_weight, self.qkv_bias, EPILOGUE_NONE, backend=rt.gemm_backend)
             store_without_rotation(qkv, ctx, binding, spec.num_heads, spec.num_kv_heads,
                                    spec.head_dim, rt.page_size)
-        group = ctx.groups[binding.group]
-        attn = torch.empty((ctx.n_tokens, self.q_size), dtype=rt.dtype, device=h.device)
-        if kernels.mma_attention_supported(rt.dtype, spec.head_dim, rt.page_size, qkv.stride(0)):
-            group_size = spec.num_heads // spec.num_kv_heads
-            # prompt portions on tcgen05 when the kernel takes the geometry, else on mma.sync
-            on_tc = _TC_ATTENTION and kernels.tc_attention_supported(rt.dtype, spec.head_dim, rt.page_size,
-                                                                     qkv.stride(0), group_size)
-            narrow, n_narrow, wide, n_wide = attention_tiles(ctx, group_size, token_tiles=on_tc)
-            for tiles, n_tiles, is_narrow in ((narrow, n_narrow, True), (wide, n_wide, False)):
-                if n_tiles == 0:
-                    continue
-                if on_tc and not is_narrow:
-                    n_splits, scratch = tc_tile_splits(ctx, n_tiles, n_narrow == 0, spec.num_heads,
-                                                           spec.num_kv_heads, spec.head_dim, spec.window)
-                    kernels.paged_attention_tc(qkv, qkv.stride(0), binding.kv, group.block_tables, ctx.cu_q,
-                                               ctx.context_lens, tiles, n_tiles, ctx.n_tokens,
-                                               spec.num_heads, spec.num_kv_heads, spec.head_dim,
-                                               spec.window, spec.scale, attn, ctx.status,
-                                               n_splits=n_splits, scratch=scratch)
-                    continue
-                alone = (n_wide == 0) if is_narrow else (n_narrow == 0)
-                if is_narrow and ctx.padded:
-                    tiles, n_tiles = None, ctx.n_seqs      # a batch of decoding requests: tile i is sequence i
-                n_splits, scratch = mma_tile_splits(ctx, n_tiles, is_narrow, alone, spec.num_heads,
-                                                    spec.num_kv_heads, spec.head_dim, spec.window)
-                kernels.paged_attention_mma(qkv, qkv.stride(0), binding.kv, group.block_tables,
-                                            ctx.cu_q, ctx.context_lens, tiles, n_tiles, is_narrow,
-                                            ctx.n_tokens, spec.num_heads, spec.num_kv_heads,
-                                            spec.head_dim, spec.window, spec.scale, attn, ctx.status,
-                                            n_splits=n_splits, scratch=scratch)
-        else:
-            n_splits, scratch = simt_splits(ctx, spec.num_heads, spec.num_kv_heads,
-                                                     spec.head_dim, spec.window)
-            kernels.paged_attention(qkv, qkv.stride(0), binding.kv, group.block_tables, ctx.tok_seq,
-                                    ctx.positions, ctx.n_tokens, spec.num_heads, spec.num_kv_heads,
-                                    spec.head_dim, spec.window, spec.scale, attn, ctx.status,
-                                    n_splits=n_splits, scratch=scratch)
+        attn = paged_attend(qkv, qkv.stride(0), ctx, binding, rt, spec.num_heads, spec.num_kv_heads, spec.head_dim,
+                            spec.window, spec.scale)
         return linear(attn, self.o_weight, self.o_bias, EPILOGUE_RESIDUAL, residual=residual,
                       out=residual, backend=rt.gemm_backend, defer_sum=getattr(ctx, "sums_may_pend", False))
+
+
+@register_part("mixer", "gated_attention")
+class GatedAttention(Mixer):
+    """Grouped-query attention with per-head RMS-normalised queries and keys, no position encoding,
+    values of a width of their own and a sigmoid gate on the concatenated heads (``GatedAttentionSpec``).
+
+    One fused product gives float rows ``[q | k | v | gate]``; one kernel normalises q and k per head in
+    float and stores k and v in the paged cache in the layout the stock attention kernels read
+    (``paged_attend``), every head padded with zeros to a common size of a multiple of 16 when the query
+    and value widths differ or are no such multiple; one kernel applies the gate and drops the padding.
+    ``forward(h, None, ...)`` returns the mixer's float output without a residual."""
+
+    capturable = True
+
+    def __init__(self, spec, runtime, prefix):
+        super().__init__(spec, runtime, prefix)
+        self.padded_dim = self.cache_head_dim(spec)
+
+    @staticmethod
+    def cache_head_dim(spec) -> int:
+        return -(-max(spec.head_dim, spec.value_dim) // 16) * 16
+
+    @classmethod
+    def _matrices(cls, spec):
+        q, kv = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
+        shapes = [(spec.query_name, (q, spec.hidden_size)), (spec.key_name, (kv, spec.hidden_size)),
+                  (spec.value_name, (spec.num_kv_heads * spec.value_dim, spec.hidden_size))]
+        if spec.gate_name is not None:
+            shapes.append((spec.gate_name, (spec.num_heads * spec.value_dim, spec.hidden_size)))
+        return shapes
+
+    @classmethod
+    def weight_specs(cls, spec, prefix):
+        specs = [WeightSpec(prefix + name, shape, role="matrix", init="weight") for name, shape in cls._matrices(spec)]
+        specs.append(WeightSpec(prefix + spec.output_name, (spec.hidden_size, spec.num_heads * spec.value_dim),
+                                role="matrix", init="weight"))
+        for name in (spec.query_norm_name, spec.key_norm_name):
+            if name is not None:
+                specs.append(WeightSpec(prefix + name, (spec.head_dim,), role="vector", init="norm_weight"))
+        return specs
+
+    @classmethod
+    def cache_request(cls, spec):
+        return KVCacheRequest(num_kv_heads=spec.num_kv_heads, head_dim=cls.cache_head_dim(spec), window=spec.window)
+
+    def load(self, fetch):
+        p, s = self.prefix, self.spec
+        self.proj_weight = torch.cat([fetch(p + name) for name, _ in self._matrices(s)])
+        self.o_weight = fetch(p + s.output_name)
+        self.q_norm = fetch(p + s.query_norm_name) if s.query_norm_name is not None else None
+        self.k_norm = fetch(p + s.key_norm_name) if s.key_norm_name is not None else None
+
+    def forward(self, h, residual, ctx, binding):
+        s, rt, hd = self.spec, self.runtime, self.padded_dim
+        if binding.kv is None:
+            raise RuntimeError("attention needs cache pages bound to it")
+        n = h.shape[0]
+        proj = linear(h, self.proj_weight, None, EPILOGUE_F32, backend=rt.gemm_backend)
+        q = torch.empty((n, s.num_heads * hd), dtype=rt.dtype, device=h.device)
+        writes = binding.writes
+        kernels.qk_norm_kv_write(proj, self.q_norm, self.k_norm, s.eps,
+                                 ctx.groups[binding.group].slots if writes else None,
+                                 binding.kv if writes else None, q, s.num_heads, s.num_kv_heads,
+                                 s.head_dim, s.value_dim, ctx.status)
+        attn = paged_attend(q, q.stride(0), ctx, binding, rt, s.num_heads, s.num_kv_heads, hd, s.window, s.scale)
+        if s.gate_name is not None:
+            gate_col = (s.num_heads + s.num_kv_heads) * s.head_dim + s.num_kv_heads * s.value_dim
+            gated = torch.empty((n, s.num_heads * s.value_dim), dtype=rt.dtype, device=h.device)
+            kernels.sigmoid_gate(attn, proj[:, gate_col:], gated, s.num_heads, s.value_dim)
+            attn = gated
+        elif hd != s.value_dim:
+            attn = attn.view(n, s.num_heads, hd)[:, :, :s.value_dim].reshape(n, -1)
+        if residual is None:
+            return linear(attn, self.o_weight, None, EPILOGUE_F32, backend=rt.gemm_backend)
+        return linear(attn, self.o_weight, None, EPILOGUE_RESIDUAL, residual=residual, out=residual,
+                      backend=rt.gemm_backend)

@@ -7,6 +7,8 @@ and each sub-layer adds into it in float.
 
 from __future__ import annotations
 
+import torch
+
 from matricxon_b200.ops.linear import PendingSum
 from matricxon_b200.parts.base import Block, build_part, register_part
 
@@ -67,4 +69,71 @@ class PreNormSequentialBlock(Block):
             ctx.sums_may_pend = False
         if isinstance(x, PendingSum) and not getattr(ctx, "pending_sum_wanted", False):
             return x.tensor()
+        return x
+
+
+@register_part("block", "post_norm_sequential")
+class PostNormSequentialBlock(Block):
+    """Norm after the sum: ``x = norm1(a x + mixer(x)); x = norm2(a x + ffn(x))`` with ``a`` the layer's
+    ``skip_scale``; a layer without a feed-forward has only the first sublayer. The sublayers read ``x``
+    itself: in the runtime dtype, which the norm that ends a sublayer writes beside the float stream
+    (``Norm.forward_scaled_sum``) and which a block hands to the next one through the step's memo; only
+    the model's first block has to round the embedding rows itself. On the 32-bit path the stream is
+    its own activation."""
+
+    def __init__(self, spec, runtime, prefix):
+        super().__init__(spec, runtime, prefix)
+        self.mixer = build_part("mixer", spec.mixer, runtime, f"{prefix}{spec.mixer_name}")
+        self.mixer_norm = build_part("norm", spec.mixer_norm, runtime, f"{prefix}{spec.mixer_norm_name}")
+        self.feed_forward = self.ffn_norm = None
+        if spec.feed_forward is not None:
+            self.feed_forward = build_part("feed_forward", spec.feed_forward, runtime,
+                                           f"{prefix}{spec.feed_forward_name}")
+            self.ffn_norm = build_part("norm", spec.ffn_norm, runtime, f"{prefix}{spec.ffn_norm_name}")
+        self.capturable = all(part.capturable for part in self.parts())
+
+    @classmethod
+    def weight_specs(cls, spec, prefix):
+        from matricxon_b200.parts.base import part_class
+
+        groups = [("mixer", spec.mixer, spec.mixer_name), ("norm", spec.mixer_norm, spec.mixer_norm_name)]
+        if spec.feed_forward is not None:
+            groups += [("feed_forward", spec.feed_forward, spec.feed_forward_name),
+                       ("norm", spec.ffn_norm, spec.ffn_norm_name)]
+        out = []
+        for category, sub, name in groups:
+            out.extend(part_class(category, sub.kind).weight_specs(sub, f"{prefix}{name}"))
+        return out
+
+    def parts(self):
+        return tuple(part for part in (self.mixer, self.mixer_norm, self.feed_forward, self.ffn_norm)
+                     if part is not None)
+
+    def load(self, fetch):
+        for part in self.parts():
+            part.load(fetch)
+
+    def _activations(self, x, ctx):
+        """The stream's rows in the runtime dtype: what the block before left, or a rounding pass."""
+        if self.runtime.dtype == torch.float32:
+            return x
+        handed = ctx.memo.get("stream_activations")
+        if handed is not None and handed[0] is x:
+            return handed[1]
+        from matricxon_b200.ops import kernels
+
+        act = torch.empty(tuple(x.shape), dtype=self.runtime.dtype, device=x.device)
+        kernels.cast_rows(x, act)
+        return act
+
+    def forward(self, x, ctx, binding):
+        if isinstance(x, PendingSum):
+            x = x.tensor()
+        h = self._activations(x, ctx)
+        mixed = self.mixer.forward(h, None, ctx, binding)
+        x, h = self.mixer_norm.forward_scaled_sum(x, mixed, self.spec.skip_scale)
+        if self.feed_forward is not None:
+            fed = self.feed_forward.forward(h, None, ctx)
+            x, h = self.ffn_norm.forward_scaled_sum(x, fed, self.spec.skip_scale)
+        ctx.memo["stream_activations"] = (x, h)
         return x

@@ -1,0 +1,81 @@
+"""Attention over one cached latent vector per token, with the per-head expansions folded around it.
+
+With c_j the normalised latent of token j and r_j its rotated shared key part, head h's score is
+``(q_plain_h . Uk_h c_j + q_rot_h . r_j) * scale = ((Uk_h^T q_plain_h) . c_j + q_rot_h . r_j) * scale``
+and its output ``Uv_h sum_j p_j c_j``: so the cache holds only ``[c_j | r_j]`` (one plane, one "head"),
+the key expansion becomes a per-head product on the query side and the value expansion a per-head
+product after the softmax. A step is: one fused product (queries and the down projection, float
+result), one kernel that normalises the latent, rotates the rotated parts and stores the token's cache
+vector, the query-side per-head product, the attention kernel over the paged latent cache, the
+value-side per-head product, and the output projection. Scores, softmax, norm and angles are float.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from matricxon_b200.ops import kernels
+from matricxon_b200.ops.linear import EPILOGUE_F32, EPILOGUE_RESIDUAL, batched_linear, linear
+from matricxon_b200.parts.base import KVCacheRequest, Mixer, build_part, register_part
+from matricxon_b200.weights.loader import WeightSpec
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention(Mixer):
+    def __init__(self, spec, runtime, prefix):
+        super().__init__(spec, runtime, prefix)
+        self.position = build_part("position", spec.position, runtime, prefix)
+        self.capturable = self.position.capturable
+        self.key_width = spec.latent_rank + spec.rot_dim
+
+    @classmethod
+    def weight_specs(cls, spec, prefix):
+        s = spec
+        matrices = {s.query_name: (s.num_heads * (s.head_dim + s.rot_dim), s.hidden_size),
+                    s.down_name: (s.latent_rank + s.rot_dim, s.hidden_size),
+                    s.key_up_name: (s.num_heads * s.head_dim, s.latent_rank),
+                    s.value_up_name: (s.num_heads * s.value_dim, s.latent_rank),
+                    s.output_name: (s.hidden_size, s.num_heads * s.value_dim)}
+        specs = [WeightSpec(prefix + name, shape, role="matrix", init="weight") for name, shape in matrices.items()]
+        specs.append(WeightSpec(prefix + s.latent_norm_name, (s.latent_rank,), role="vector", init="norm_weight"))
+        return specs
+
+    @classmethod
+    def cache_request(cls, spec):
+        # one vector per token for all heads: the latent, then the rotated shared key part
+        return KVCacheRequest(num_kv_heads=1, head_dim=spec.latent_rank + spec.rot_dim, window=spec.window,
+                              planes=1)
+
+    def load(self, fetch):
+        p, s = self.prefix, self.spec
+        self.proj_weight = torch.cat([fetch(p + s.query_name), fetch(p + s.down_name)])
+        self.latent_norm = fetch(p + s.latent_norm_name)
+        # Uk as [head][rank][dim]: the query-side product is q_plain_h @ Uk_h, i.e. "weight" Uk_h^T
+        self.key_up_t = fetch(p + s.key_up_name).view(s.num_heads, s.head_dim, s.latent_rank) \
+                                                .transpose(1, 2).contiguous()
+        self.value_up = fetch(p + s.value_up_name).view(s.num_heads, s.value_dim, s.latent_rank).contiguous()
+        self.o_weight = fetch(p + s.output_name)
+
+    def forward(self, h, residual, ctx, binding):
+        s, rt = self.spec, self.runtime
+        if binding.kv is None:
+            raise RuntimeError("latent attention needs cache pages bound to it")
+        n, heads, rank = h.shape[0], s.num_heads, s.latent_rank
+        proj = linear(h, self.proj_weight, None, EPILOGUE_F32, backend=rt.gemm_backend)
+        q_plain = torch.empty((n, heads * s.head_dim), dtype=rt.dtype, device=h.device)
+        q_lat = torch.empty((n, heads, self.key_width), dtype=rt.dtype, device=h.device)
+        writes = binding.writes
+        kernels.latent_prepare(proj, ctx.positions, self.position.frequencies, self.position.amplitude,
+                               self.latent_norm, s.eps, ctx.groups[binding.group].slots if writes else None,
+                               binding.kv if writes else None, q_plain, q_lat, heads, s.head_dim, s.rot_dim,
+                               s.position.rotary_dim, rank, ctx.status)
+        batched_linear(q_plain.view(n, heads, s.head_dim), self.key_up_t, None, q_lat[:, :, :rank])
+        mixed = torch.empty((n, heads, rank), dtype=rt.dtype, device=h.device)
+        kernels.latent_attention(q_lat, binding.kv, ctx.groups[binding.group].block_tables, ctx.tok_seq,
+                                 ctx.positions, rank, s.window, s.scale, mixed, ctx.status)
+        attn = torch.empty((n, heads * s.value_dim), dtype=rt.dtype, device=h.device)
+        batched_linear(mixed, self.value_up, None, attn.view(n, heads, s.value_dim))
+        if residual is None:
+            return linear(attn, self.o_weight, None, EPILOGUE_F32, backend=rt.gemm_backend)
+        return linear(attn, self.o_weight, None, EPILOGUE_RESIDUAL, residual=residual, out=residual,
+                      backend=rt.gemm_backend)

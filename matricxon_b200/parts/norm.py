@@ -45,3 +45,40 @@ class LayerNorm(Norm):
         out = torch.empty(tuple(x.shape), dtype=self.runtime.dtype, device=x.device)
         kernels.layernorm_sum(x, pending.acc, pending.bias, self.weight, self.bias, self.spec.eps, out)
         return x, out
+
+
+@register_part("norm", "rmsnorm")
+class RmsNorm(Norm):
+    """``x / sqrt(mean(x^2) + eps) * scale`` with float statistics; the stored weight is the scale or,
+    with ``unit_offset``, the scale minus one. Beside the plain form it ends a post-norm sublayer in one
+    kernel: ``forward_scaled_sum`` forms ``skip_scale * x + sublayer``, normalises it into the residual
+    stream and hands the next sublayer its input in the runtime dtype."""
+
+    capturable = True
+
+    @classmethod
+    def weight_specs(cls, spec, prefix):
+        # a weight stored around zero is drawn like a norm's shift when random weights are asked for
+        init = "norm_bias" if spec.unit_offset else "norm_weight"
+        return [WeightSpec(prefix + spec.weight_name, (spec.size,), role="vector", init=init)]
+
+    def load(self, fetch):
+        self.weight = fetch(self.prefix + self.spec.weight_name)
+        self.offset = 1.0 if self.spec.unit_offset else 0.0
+
+    def forward(self, x, out=None, rows=None):
+        n_rows = x.shape[0] if rows is None else rows.numel()
+        if out is None:
+            out = torch.empty((n_rows, self.spec.size), dtype=self.runtime.dtype, device=x.device)
+        kernels.rmsnorm(x, self.weight, self.offset, self.spec.eps, out, rows)
+        return out
+
+    def forward_scaled_sum(self, x, sublayer, skip_scale):
+        """``x <- norm(skip_scale * x + sublayer)`` in place (both float32). Returns (x, activations): the
+        same rows in the runtime dtype, which is ``x`` itself on the 32-bit path."""
+        if self.runtime.dtype == torch.float32:
+            kernels.rmsnorm_sum(x, sublayer, skip_scale, self.weight, self.offset, self.spec.eps)
+            return x, x
+        act = torch.empty(tuple(x.shape), dtype=self.runtime.dtype, device=x.device)
+        kernels.rmsnorm_sum(x, sublayer, skip_scale, self.weight, self.offset, self.spec.eps, act)
+        return x, act

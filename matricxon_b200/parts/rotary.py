@@ -62,3 +62,47 @@ def store_without_rotation(qkv, ctx, binding, n_heads, n_kv_heads, head_dim, pag
     empty = torch.empty(0, dtype=torch.float32, device=qkv.device)
     kernels.rope_kv_write(qkv, ctx.positions, empty, ctx.groups[binding.group].slots, binding.kv,
                           n_heads, n_kv_heads, head_dim, 0, page_size, ctx.status)
+
+
+def interpolated_frequencies(spec) -> tuple[torch.Tensor, float]:
+    """(frequency per pair, factor on cos and sin) of an ``InterpolatedRotarySpec``, in float64 on the host.
+
+    With D = rotary_dim and base theta, pair i turns ``f_i = theta^(-2i/D)`` radians a position. The pair
+    that makes t turns within the original context has index ``d(t) = D ln(original / (2 pi t)) / (2 ln theta)``.
+    Pairs below ``lo = max(floor(d(fast)), 0)`` keep f_i, pairs above ``hi = min(ceil(d(slow)), D - 1)`` get
+    ``f_i / factor``, and those between are blended with ``ramp = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)``."""
+    import math
+
+    dims, half = spec.rotary_dim, spec.rotary_dim // 2
+    freq = [spec.theta ** (-2.0 * i / dims) for i in range(half)]
+    if spec.factor is None:
+        return torch.tensor(freq, dtype=torch.float64), 1.0
+
+    def pair_of(turns: float) -> float:
+        return dims * math.log(spec.original / (2.0 * math.pi * turns)) / (2.0 * math.log(spec.theta))
+
+    lo = max(math.floor(pair_of(spec.fast)), 0)
+    hi = min(math.ceil(pair_of(spec.slow)), dims - 1)
+    out = []
+    for i, f in enumerate(freq):
+        ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+        out.append(f / spec.factor * ramp + f * (1.0 - ramp))
+    return torch.tensor(out, dtype=torch.float64), 0.1 * math.log(spec.factor) + 1.0
+
+
+@register_part("position", "rotary_interpolated")
+class InterpolatedRotary(PositionEncoding):
+    """Rotary encoding with stretched frequencies and an amplitude on cos and sin. It holds the table
+    (``frequencies`` float32 on the device, ``amplitude``) for mixers whose own kernels rotate (latent
+    attention rotates a part of each query head and one shared key part); the whole-head
+    ``rotate_and_store`` of the stock attention part knows no amplitude and is not offered."""
+
+    capturable = True
+
+    def __init__(self, spec, runtime, prefix):
+        super().__init__(spec, runtime, prefix)
+        table, self.amplitude = interpolated_frequencies(spec)
+        self.frequencies = table.to(torch.float32).to(runtime.device)
+
+    def rotate_and_store(self, qkv, ctx, binding, n_heads, n_kv_heads, head_dim):
+        raise NotImplementedError("an interpolated rotary table serves mixers that rotate in their own kernels")

@@ -89,8 +89,160 @@ class MlpSpec:
 
 
 @dataclass(frozen=True)
+class RmsNormSpec:
+    """``x / sqrt(mean(x^2) + eps) * scale`` over the last axis, eps inside the root. ``unit_offset``:
+    the checkpoint stores ``scale - 1`` (a weight around zero). The tensor is called
+    ``<prefix><weight_name>``; an empty ``weight_name`` makes the prefix itself the tensor's name."""
+
+    size: int
+    eps: float
+    unit_offset: bool = False
+    weight_name: str = "weight"
+    kind: str = "rmsnorm"
+
+
+@dataclass(frozen=True)
+class InterpolatedRotarySpec:
+    """Rotary encoding of the first ``rotary_dim`` entries of a vector, halves paired as
+    (i, i + rotary_dim/2), whose frequencies are stretched for contexts longer than the ``original`` one:
+    pair i keeps ``theta^(-2i/rotary_dim)`` when it turns more than ``fast`` times within the original
+    context, is divided by ``factor`` when it turns fewer than ``slow`` times, and is blended linearly in
+    between; cos and sin are multiplied by ``0.1 ln(factor) + 1``. ``factor`` None: plain frequencies."""
+
+    rotary_dim: int
+    theta: float
+    factor: float | None = None
+    original: float = 0.0
+    fast: float = 32.0
+    slow: float = 1.0
+    kind: str = "rotary_interpolated"
+
+    def __post_init__(self) -> None:
+        if self.rotary_dim < 0 or self.rotary_dim % 2:
+            raise ValueError(f"a rotary encoding pairs dimensions: {self.rotary_dim} is odd or negative")
+        if self.factor is not None and not (self.factor > 0 and self.original > 0 and self.fast > 0 and self.slow > 0):
+            raise ValueError("frequency interpolation needs positive factor, original, fast and slow")
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Attention whose keys and values are expanded per head from one cached latent vector per token.
+
+    A query head is ``[head_dim plain | rot_dim rotated]``; the down projection gives ``latent_rank``
+    entries (RMS-normalised with a plain weight: the latent) and ``rot_dim`` more (one rotated key
+    part shared by all heads). Head h's plain key is ``Uk_h latent``, its value ``Uv_h latent``
+    (``value_dim`` wide); scores are ``(q_plain . k_plain + q_rot . k_rot) * scale`` under the window
+    rule of ``AttentionSpec``. Names are full tensor names under the mixer's prefix."""
+
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    rot_dim: int
+    value_dim: int
+    latent_rank: int
+    window: int | None
+    scale: float
+    eps: float
+    position: Any                      # how the rot_dim parts are rotated
+    query_name: str
+    down_name: str
+    latent_norm_name: str
+    key_up_name: str
+    value_up_name: str
+    output_name: str
+    kind: str = "latent_attention"
+
+    def __post_init__(self) -> None:
+        if min(self.num_heads, self.head_dim, self.value_dim, self.latent_rank) <= 0 or self.rot_dim < 0:
+            raise ValueError("latent attention needs positive head count, head sizes and latent rank")
+        if self.position is not None and self.position.rotary_dim > self.rot_dim:
+            raise ValueError(f"{self.position.rotary_dim} rotated dimensions exceed the rotated part of {self.rot_dim}")
+
+
+@dataclass(frozen=True)
+class GatedAttentionSpec:
+    """Grouped-query attention without position encoding: queries and keys are RMS-normalised per head
+    (one plain weight of ``head_dim`` entries for all query heads, one for all key heads; None: no norm),
+    values are ``value_dim`` wide, and the concatenated heads are multiplied by ``sigmoid(gate(h))``
+    before the output projection (``gate_name`` None: no gate). Window rule as ``AttentionSpec``."""
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    window: int | None
+    scale: float
+    eps: float
+    query_name: str
+    key_name: str
+    value_name: str
+    output_name: str
+    gate_name: str | None = None
+    query_norm_name: str | None = None
+    key_norm_name: str | None = None
+    kind: str = "gated_attention"
+
+    def __post_init__(self) -> None:
+        if self.num_kv_heads <= 0 or self.num_heads % self.num_kv_heads != 0:
+            raise ValueError(f"{self.num_heads} attention heads are no multiple of {self.num_kv_heads} kv heads")
+        if self.head_dim <= 0 or self.value_dim <= 0 or max(self.head_dim, self.value_dim) > 256:
+            raise ValueError(f"head sizes {self.head_dim} / {self.value_dim} are outside 1..256: "
+                             "no attention kernel of this engine takes them")
+
+
+@dataclass(frozen=True)
+class RglruSpec:
+    """A gated linear recurrence behind a short causal convolution, times a GELU branch.
+
+    ``y = gelu_tanh(Wy h + by)``, ``u = conv(Wx h + bx)`` (``taps`` per channel, the last tap on the
+    current token); per block b of ``width / blocks`` channels ``r = sigmoid(Ra_b u_b + ba_b)`` and
+    ``i = sigmoid(Ri_b u_b + bi_b)``; ``a = exp(-decay * r * softplus(lambda))``,
+    ``S <- a S + sqrt(1 - a^2) i u`` from S = 0; the mixer's output is ``Wo (S * y)``."""
+
+    hidden_size: int
+    width: int
+    blocks: int
+    taps: int
+    decay: float
+    gate_branch_name: str              # y
+    recurrent_branch_name: str         # x
+    conv_name: str
+    recurrence_gate_name: str
+    input_gate_name: str
+    lambda_name: str
+    output_name: str
+    bias_suffix: str = ".b"
+    kind: str = "rglru"
+
+    def __post_init__(self) -> None:
+        if self.blocks <= 0 or self.width <= 0 or self.width % self.blocks:
+            raise ValueError(f"a recurrence of {self.width} channels cannot be cut into {self.blocks} equal blocks")
+        if self.taps < 1:
+            raise ValueError("the convolution needs at least one tap")
+
+
+@dataclass(frozen=True)
+class ClampedGluSpec:
+    """``down(g * sigmoid(slope * g) * (u + shift))`` with ``g = min(gate(h), limit)`` and
+    ``u = clamp(up(h), -limit, limit)``; ``limit`` None leaves both unclamped. No biases."""
+
+    hidden_size: int
+    intermediate_size: int
+    limit: float | None
+    gate_name: str
+    up_name: str
+    down_name: str
+    slope: float = 1.702
+    shift: float = 1.0
+    kind: str = "clamped_glu"
+
+
+@dataclass(frozen=True)
 class LayerSpec:
-    """One decoder layer: which block arrangement holds which parts."""
+    """One decoder layer: which block arrangement holds which parts. ``feed_forward`` (with its norm)
+    may be None for blocks that can do without; ``skip_scale`` is the weight of the skip path in blocks
+    that have one (``norm(skip_scale * x + sublayer(x))``)."""
 
     mixer: Any
     feed_forward: Any
@@ -102,6 +254,7 @@ class LayerSpec:
     mixer_norm_name: str
     ffn_norm_name: str
     block: str = "pre_norm_sequential"
+    skip_scale: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -139,6 +292,12 @@ class ModelSpec:
     embedding_scale: float = 1.0
     head_bias: bool = False
     logit_softcap: float | None = None
+    # how names are put together: "<embedding_name><weight_suffix>", a layer's prefix from
+    # ``layer_prefix_format`` (fields {prefix} and {index}), the final norm's prefix (None:
+    # "<final_norm_name>.")
+    weight_suffix: str = ".weight"
+    layer_prefix_format: str = "{prefix}.{index}."
+    final_norm_prefix: str | None = None
     extra: dict = field(default_factory=dict, compare=False, hash=False)
 
     def __post_init__(self) -> None:
@@ -153,6 +312,14 @@ class ModelSpec:
                 if self.schedule[entry.cache_of].cache_of is not None:
                     raise ValueError(f"schedule entry {position} reads the cache of entry "
                                      f"{entry.cache_of}, which owns no cache itself")
+
+
+    def layer_prefix_of(self, index: int) -> str:
+        return self.layer_prefix_format.format(prefix=self.layer_prefix, index=index)
+
+    @property
+    def norm_prefix(self) -> str:
+        return f"{self.final_norm_name}." if self.final_norm_prefix is None else self.final_norm_prefix
 
 
 def sequential_schedule(num_layers: int) -> tuple[ScheduleEntry, ...]:
