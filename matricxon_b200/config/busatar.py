@@ -108,8 +108,8 @@ class BusatarLayer:
         if kind == "latent_attention":
             rot_dim = m.integer("rot_dim", minimum=0)
             rot = BusatarRotary.from_dict(mixer.get("rot"), where + ".mixer.rot")
-            if rot.dims != rot_dim:
-                raise ConfigError(f"{where}.mixer: rot.dims ({rot.dims}) must equal rot_dim ({rot_dim})")
+            if rot.dims > rot_dim:
+                raise ConfigError(f"{where}.mixer: rot.dims ({rot.dims}) exceeds rot_dim ({rot_dim})")
             fields.update(rot_dim=rot_dim, kv_rank=m.integer("kv_rank", minimum=1), rot=rot)
         elif kind == "attention":
             fields.update(kv_heads=m.integer("kv_heads", minimum=1))

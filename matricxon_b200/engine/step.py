@@ -408,9 +408,16 @@ class StepRunner:
         launches_before = kernels.launch_count
         # steps of very few rows gain from kernels that start while their predecessor drains
         kernels.set_chained_launch(chained)
+        # The warm-up below runs the step for real and the caller replays the captured graph afterwards, so
+        # the step runs twice. Writing the same keys and values twice changes nothing, but a recurrent state
+        # would move two tokens ahead: the state slots of the step's requests are put back after the warm-up.
+        slots = sorted(set(ctx.host.state_slots))
+        kept = [(state, state[slots].clone()) for state in self.storage.states if state is not None]
         try:
             self._forward(ctx, decode_rows=decode_rows)             # warm-up, outside the capture
             launches = kernels.launch_count - launches_before
+            for state, before in kept:
+                state[slots] = before
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             ctx.capturing = True
