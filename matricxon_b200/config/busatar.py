@@ -159,6 +159,11 @@ class BusatarConfig:
     max_positions: int = DEFAULT_MAX_POSITIONS
 
     architecture = "Busatar"
+    model_type = "busatar"
+
+    @property
+    def vocab_size(self) -> int:
+        return self.vocab
 
     @classmethod
     def from_dict(cls, raw: dict[str, Any], where: str = "config.json") -> "BusatarConfig":
