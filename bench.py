@@ -322,6 +322,150 @@ def run_workload(tag: str, config_dict: dict, prompt_lens: list[int], decode_ste
     return out
 
 
+# ---------------------------------------------------------------- --compare busatar
+# Busatar at layer sizes of real models beside StarCoder2 at equal width, head count, layer count and
+# feed-forward parameter count (its ungated feed-forward gets 1.5 times the gated one's width).
+COMPARE_SIZES = {
+    "w1024": dict(width=1024, heads=8, dim=64, rot=32, rank=256, ff=4096, blocks=8),
+    "w2048": dict(width=2048, heads=16, dim=128, rot=64, rank=512, ff=8192, blocks=16),
+}
+COMPARE_LAYERS = 8
+COMPARE_VOCAB = 32768
+COMPARE_WINDOW = 4096
+
+
+def busatar_config(size: dict) -> dict:
+    w, h = size["width"], size["heads"]
+    mlp = {"kind": "dense", "ff": size["ff"], "limit": 7.0}
+    rot = {"base": 10000.0, "dims": size["rot"],
+           "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    latent = {"type": "latent_attention", "mlp": mlp,
+              "mixer": {"heads": h, "dim": size["dim"], "rot_dim": size["rot"], "kv_rank": size["rank"],
+                        "vdim": size["dim"], "mask": {"size": COMPARE_WINDOW},
+                        "scale": (size["dim"] + size["rot"]) ** -0.5, "rot": rot}}
+    attention = {"type": "attention", "mlp": mlp,
+                 "mixer": {"heads": h, "kv_heads": 4, "dim": 128, "vdim": 128, "mask": {"size": COMPARE_WINDOW},
+                           "scale": 128 ** -0.5}}
+    recurrence = {"type": "rglru", "mlp": mlp, "mixer": {"width": w, "blocks": size["blocks"], "conv": 4}}
+    pattern = [latent, latent, attention, recurrence]
+    return {"architecture": "Busatar", "vocab": COMPARE_VOCAB, "width": w, "postln_alpha": 2.0,
+            "norm": {"eps": 1e-5}, "layers": [pattern[i % 4] for i in range(COMPARE_LAYERS)]}
+
+
+def starcoder2_like(size: dict) -> dict:
+    return dict(STARCODER2_3B, num_hidden_layers=COMPARE_LAYERS, hidden_size=size["width"],
+                num_attention_heads=size["width"] // 128, num_key_value_heads=4, head_dim=128,
+                intermediate_size=size["ff"] * 3 // 2, vocab_size=COMPARE_VOCAB,
+                sliding_window=COMPARE_WINDOW, max_position_embeddings=16384, tie_word_embeddings=False)
+
+
+def measure_design(raw: dict, context: int, batches: list[int], steps: int, warmup: int,
+                   use_graphs: bool = True) -> dict:
+    """Prefill of one 2,048-token prompt in one step and in 512-token steps, and decode steps at several
+    batch sizes after ``context`` cached tokens, all timed on the device with CUDA events."""
+    import torch
+
+    from matricxon_b200 import ChatEngine
+    from matricxon_b200.config.registry import config_from_dict
+    from matricxon_b200.engine.core import build_model
+    from matricxon_b200.engine.step import StepEntry
+    from matricxon_b200.weights.random_init import RandomInit, RandomSource, weight_specs_for
+
+    config = config_from_dict(json.loads(json.dumps(raw)))
+    source = RandomSource(weight_specs_for(config), seed=0, init=RandomInit(weight_std=0.02, bias_std=0.02),
+                          device="cuda:0", store_dtype=torch.bfloat16)
+    model = build_model(config, source, "bfloat16", "cuda:0", PAGE_SIZE)
+    weight_bytes = sum(t.numel() * t.element_size() for t in _model_tensors(model))
+    engine = ChatEngine(model, max_cache_tokens=max(batches) * (COMPARE_WINDOW + 2048), max_active=max(batches),
+                        max_batched_tokens=8192, prefill_chunk=PREFILL_TOKENS, max_model_len=2 * COMPARE_WINDOW,
+                        use_graphs=use_graphs)
+    vocab = config.vocab_size
+    runner, cache = engine.core.runner, engine.core.cache
+    generator = torch.Generator().manual_seed(3)
+    prompt = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=generator).tolist()
+    out = {"weight_bytes": weight_bytes, "cache_bytes_per_token": engine.core.bytes_per_token}
+    for name, portion in (("prefill_2048", PREFILL_TOKENS), ("prefill_2048_in_512", 512)):
+        times = []
+        for rep in range(5):
+            cache.add_request("p")
+            torch.cuda.synchronize()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            for start in range(0, PREFILL_TOKENS, portion):
+                last = start + portion >= PREFILL_TOKENS
+                runner.run([StepEntry("p", prompt[start:start + portion], [portion - 1] if last else [])])
+            end.record()
+            torch.cuda.synchronize()
+            cache.free_request("p")
+            if rep >= 2:
+                times.append(begin.elapsed_time(end))
+        ms = sorted(times)[len(times) // 2]
+        out[name + "_ms"] = round(ms, 3)
+        out[name + "_tok_s"] = round(PREFILL_TOKENS / (ms * 1e-3), 1)
+    for batch in batches:
+        ids = fill_cache(engine, batch, context, vocab)
+        ms = time_decode(engine, ids, vocab, steps, warmup)
+        out[f"decode_b{batch}_ms"] = round(ms, 4)
+        out[f"decode_b{batch}_tok_s"] = round(batch / (ms * 1e-3), 1)
+        out[f"decode_b{batch}_launches"] = runner.launches_per_step
+        for rid in ids:
+            cache.free_request(rid)
+    runner.check_status()
+    del engine, model, source
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
+
+
+def _model_tensors(model):
+    """Every device tensor a model's parts hold (its weights as they are kept for the kernels)."""
+    import torch
+
+    seen, stack, found = set(), [model], []
+    while stack:
+        item = stack.pop()
+        if id(item) in seen:
+            continue
+        seen.add(id(item))
+        if isinstance(item, torch.Tensor):
+            if item.is_cuda:
+                found.append(item)
+        elif isinstance(item, (list, tuple)):
+            stack.extend(item)
+        elif hasattr(item, "__dict__") and type(item).__module__.startswith("matricxon_b200"):
+            stack.extend(v for k, v in vars(item).items() if k not in ("bindings", "runtime", "spec"))
+    unique = {t.data_ptr(): t for t in found}
+    return list(unique.values())
+
+
+def compare_designs(args) -> int:
+    import torch
+
+    if not torch.cuda.is_available():
+        print("bench.py: no CUDA device")
+        return 1
+    peaks, peak_source = load_peaks()
+    clocks = ClockSampler()
+    clocks.start()
+    sizes = [s for s in args.compare_sizes.split(",") if s]
+    batches = [int(b) for b in args.compare_batches.split(",")]
+    record = {"compare": "busatar vs starcoder2 at equal sizes", "layers": COMPARE_LAYERS, "vocab": COMPARE_VOCAB,
+              "window": COMPARE_WINDOW, "context": args.context, "dtype": "bf16", "steps": args.steps,
+              "warmup": max(args.warmup, 3), "peaks": peak_source, "hbm_gbs": peaks["hbm_gbs"],
+              "data": "synthetic: seeded random weights, uniform random token ids", "sizes": {}}
+    for name in sizes:
+        size = COMPARE_SIZES[name]
+        entry = {}
+        for design, raw in (("busatar", busatar_config(size)), ("starcoder2", starcoder2_like(size))):
+            entry[design] = measure_design(raw, args.context, batches, args.steps, max(args.warmup, 3),
+                                           use_graphs=not args.no_graphs)
+        record["sizes"][name] = entry
+    clocks.stop()
+    record["clocks"] = clocks.summary()
+    print(json.dumps(record))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -339,6 +483,11 @@ def main() -> int:
                         help="leave out the 7B and 15B workloads through the scheduler")
     parser.add_argument("--no-graphs", action="store_true",
                         help="launch every kernel of a decode step by itself (for profilers)")
+    parser.add_argument("--compare", choices=["busatar"], default=None,
+                        help="instead of the headline workload: Busatar beside StarCoder2 at equal layer sizes "
+                             "(prefill and decode throughput at a few sizes)")
+    parser.add_argument("--compare-sizes", default="w1024,w2048")
+    parser.add_argument("--compare-batches", default="1,8,32")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
@@ -347,6 +496,8 @@ def main() -> int:
         return reference_arm(args)
     if args.warmup < 3:
         args.warmup = 3
+    if args.compare:
+        return compare_designs(args)
 
     import torch
 

@@ -11,7 +11,7 @@
 //   portion's first token come from the state. Writes u as float and, when asked, a copy in the
 //   activation dtype (the gate product's operand).
 // mx_rglru_scan (one thread per (sequence, channel), tokens in order):
-//   r = sigmoid(gates[t][b][j]), i = sigmoid(gates[t][b][bw + j])     (channel c = b * bw + j)
+//   r = sigmoid(gates[t][b][j] + bias[b][j]), i = sigmoid(gates[t][b][bw + j] + bias[b][bw + j])   (c = b * bw + j)
 //   log a = -decay * r * softplus(lambda[c]);  a = exp(log a)
 //   S <- a * S + sqrt(1 - a^2) * i * u[t][c];   out[t][c] = S * gelu_tanh(y[t][c])
 //   then stores S and the last taps-1 inputs. Everything is float; only `out` is rounded.
@@ -50,7 +50,8 @@ __global__ void causal_conv_kernel(const float* __restrict__ xy, int ld, int x_c
 template <typename T>
 __global__ void rglru_scan_kernel(const float* __restrict__ xy, int ld, int x_col, int y_col,
                                   const float* __restrict__ u, const float* __restrict__ gates,
-                                  const float* __restrict__ lambda, float decay, float* __restrict__ state,
+                                  const float* __restrict__ gate_bias, const float* __restrict__ lambda,
+                                  float decay, float* __restrict__ state,
                                   const int* __restrict__ cu_q, const int* __restrict__ state_slots,
                                   T* __restrict__ out, int width, int block_width, int taps) {
     const int seq = blockIdx.x;
@@ -61,14 +62,16 @@ __global__ void rglru_scan_kernel(const float* __restrict__ xy, int ld, int x_co
     float* st = state + (size_t)state_slots[seq] * taps * width;
     const int b = c / block_width, j = c - b * block_width;
     const size_t gate_col = (size_t)b * 2 * block_width + j;
+    const float bias_r = gate_bias ? gate_bias[gate_col] : 0.f;
+    const float bias_i = gate_bias ? gate_bias[gate_col + block_width] : 0.f;
     const float lam = lambda[c];
     const float rate = -decay * (lam > 20.f ? lam : log1pf(expf(lam)));
     float s = st[(size_t)(taps - 1) * width + c];
     for (int k = 0; k < n; ++k) {
         const size_t t = (size_t)(t0 + k);
         const float* g = gates + t * 2 * width + gate_col;
-        const float r = 1.0f / (1.0f + expf(-g[0]));
-        const float i = 1.0f / (1.0f + expf(-g[block_width]));
+        const float r = 1.0f / (1.0f + expf(-(g[0] + bias_r)));
+        const float i = 1.0f / (1.0f + expf(-(g[block_width] + bias_i)));
         const float log_a = rate * r;
         const float a = expf(log_a);
         const float drive = sqrtf(-expm1f(2.0f * log_a));
@@ -106,7 +109,7 @@ extern "C" int mx_causal_conv(const float* xy, int ld, int x_col, const float* c
 }
 
 extern "C" int mx_rglru_scan(const float* xy, int ld, int x_col, int y_col, const float* u, const float* gates,
-                             const float* lambda, float decay, float* state, const int* cu_q,
+                             const float* gate_bias, const float* lambda, float decay, float* state, const int* cu_q,
                              const int* state_slots, void* out, int out_dtype, int n_seqs, int width,
                              int block_width, int taps, cudaStream_t stream) {
     if (n_seqs <= 0) return MX_OK;
@@ -114,12 +117,12 @@ extern "C" int mx_rglru_scan(const float* xy, int ld, int x_col, int y_col, cons
     const int threads = 64;
     dim3 grid(n_seqs, (width + threads - 1) / threads);
     if (out_dtype == MX_DTYPE_F32)
-        rglru_scan_kernel<float><<<grid, threads, 0, stream>>>(xy, ld, x_col, y_col, u, gates, lambda, decay, state,
-                                                              cu_q, state_slots, (float*)out, width, block_width,
+        rglru_scan_kernel<float><<<grid, threads, 0, stream>>>(xy, ld, x_col, y_col, u, gates, gate_bias, lambda, decay,
+                                                              state, cu_q, state_slots, (float*)out, width, block_width,
                                                               taps);
     else
-        rglru_scan_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(xy, ld, x_col, y_col, u, gates, lambda, decay,
-                                                                      state, cu_q, state_slots,
+        rglru_scan_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(xy, ld, x_col, y_col, u, gates, gate_bias, lambda,
+                                                                      decay, state, cu_q, state_slots,
                                                                       (__nv_bfloat16*)out, width, block_width, taps);
     return mx_launch_status();
 }

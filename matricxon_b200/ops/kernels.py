@@ -628,6 +628,58 @@ def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, block_tables: tor
     _launched()
 
 
+def latent_attention_mma_supported(dtype: torch.dtype, rank: int, dk: int) -> bool:
+    """Whether the tensor-core latent attention takes this geometry (bfloat16, rank a multiple of 32 up to
+    512, key width a multiple of 16 that fits in shared memory)."""
+    return dtype == torch.bfloat16 and bool(library().mx_latent_attention_mma_supported(rank, dk))
+
+
+def latent_tile_list(q_lens: list[int], n_heads: int) -> list[int]:
+    """(sequence, first row) of the 64-row tiles of the (token, head) rows of sequences that bring
+    ``q_lens`` tokens, flattened; the tiles of a sequence's latest tokens first (they walk the most keys)."""
+    tiles: list[int] = []
+    for seq, q_len in enumerate(q_lens):
+        rows = q_len * n_heads
+        for row in range((rows - 1) // 64 * 64, -1, -64):
+            tiles.extend((seq, row))
+    return tiles
+
+
+def latent_attention_mma(q_lat: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor,
+                         cu_q: torch.Tensor, context_lens: torch.Tensor, tiles: torch.Tensor | None,
+                         n_tiles: int, rank: int, window: int | None, scale: float, out: torch.Tensor,
+                         status: torch.Tensor, n_splits: int = 1, scratch: torch.Tensor | None = None) -> None:
+    """``latent_attention`` on the tensor cores (bfloat16). ``tiles`` is int32 [n_tiles, 2] from
+    ``latent_tile_list``; None means that tile i is sequence i (a fixed-size batch of decoding requests,
+    ``n_tiles`` sequences). ``n_splits`` > 1 shares every tile's keys out between that many blocks;
+    ``scratch`` (float32, ``attention_scratch_bytes(tokens, heads, rank, n_splits)``) takes their parts."""
+    _need(q_lat, "q_lat", torch.bfloat16)
+    _need(cache, "cache", torch.bfloat16)
+    _need(out, "out", torch.bfloat16)
+    for name, tensor in (("block_tables", block_tables), ("cu_q", cu_q), ("context_lens", context_lens),
+                         ("status", status)):
+        _need(tensor, name, torch.int32)
+    n, n_heads, dk = q_lat.shape
+    assert tuple(cache.shape[1:3]) == (1, 1) and cache.shape[4] == dk, cache.shape
+    assert tuple(out.shape) == (n, n_heads, rank)
+    if tiles is not None:
+        _need(tiles, "tiles", torch.int32)
+        assert tiles.numel() >= 2 * n_tiles
+    else:
+        assert n_tiles <= context_lens.numel()
+    if n_splits > 1:
+        need = attention_scratch_bytes(n, n_heads, rank, n_splits)
+        if scratch is None or scratch.numel() * scratch.element_size() < need:
+            raise KernelLibraryError(f"latent attention with {n_splits} splits needs {need} bytes of scratch")
+        _need(scratch, "scratch", torch.float32)
+    check(library().mx_latent_attention_mma(
+        _ptr(q_lat), _ptr(cache), cache.shape[0], cache.shape[3], _ptr(block_tables), block_tables.stride(0),
+        _ptr(cu_q), _ptr(context_lens), _ptr(tiles), n_tiles, (n_heads + 63) // 64, n, n_heads, rank, dk,
+        int(window or 0), float(scale), _ptr(out), int(n_splits), _ptr(scratch) if n_splits > 1 else None,
+        _ptr(status), _stream()), "latent_attention_mma")
+    _launched(2 if n_splits > 1 else 1)
+
+
 # ---------------------------------------------------------------------- normalised, gated attention
 def qk_norm_kv_write(proj: torch.Tensor, q_weight: torch.Tensor | None, k_weight: torch.Tensor | None,
                      eps: float, slots: torch.Tensor | None, cache: torch.Tensor | None, q_out: torch.Tensor,
@@ -707,17 +759,22 @@ def causal_conv(xy: torch.Tensor, x_col: int, conv_weight: torch.Tensor, conv_bi
 
 
 def rglru_scan(xy: torch.Tensor, x_col: int, y_col: int, u: torch.Tensor, gates: torch.Tensor,
-               lam: torch.Tensor, decay: float, state: torch.Tensor, cu_q: torch.Tensor,
-               state_slots: torch.Tensor, n_seqs: int, block_width: int, out: torch.Tensor) -> None:
+               gate_bias: torch.Tensor | None, lam: torch.Tensor, decay: float, state: torch.Tensor,
+               cu_q: torch.Tensor, state_slots: torch.Tensor, n_seqs: int, block_width: int,
+               out: torch.Tensor) -> None:
     """The gated recurrence over every sequence's tokens in order, from and to ``state``; ``gates`` is
-    float32 [tokens, blocks, 2 * block_width] (recurrence gate, then input gate, before their sigmoids)."""
+    float32 [tokens, blocks, 2 * block_width] (recurrence gate, then input gate, before their sigmoids and,
+    when ``gate_bias`` [blocks, 2 * block_width] is given, before their biases)."""
     for name, tensor in (("xy", xy), ("u", u), ("gates", gates), ("lambda", lam), ("state", state)):
         _need(tensor, name, torch.float32)
+    if gate_bias is not None:
+        _need(gate_bias, "gate_bias", torch.float32)
+        assert gate_bias.numel() == 2 * u.shape[1]
     _need(out, "out")
     n, width = u.shape
     taps = state.shape[1]
     assert gates.numel() == n * 2 * width and tuple(out.shape) == (n, width) and lam.numel() == width
-    check(library().mx_rglru_scan(_ptr(xy), xy.stride(0), x_col, y_col, _ptr(u), _ptr(gates), _ptr(lam),
+    check(library().mx_rglru_scan(_ptr(xy), xy.stride(0), x_col, y_col, _ptr(u), _ptr(gates), _ptr(gate_bias), _ptr(lam),
                                   float(decay), _ptr(state), _ptr(cu_q), _ptr(state_slots), _ptr(out),
                                   dtype_code(out.dtype), n_seqs, width, block_width, taps, _stream()),
           "rglru_scan")

@@ -189,8 +189,33 @@ def batched_linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | N
     side in a row); weight [B, N, K] in the dtype of x; bias float32 [B, N]; out in the dtype of x or float32."""
     if x.shape[0] == 0:
         return out
+    if x.dtype == torch.bfloat16 and bias is None and x.shape[0] > 32:
+        # many rows: the library's strided batched product (float accumulator kept for a float result),
+        # then one strided copy into the caller's interleaved layout
+        acc = _bmm(x.transpose(0, 1), weight.transpose(1, 2), out.dtype)
+        if acc is not None:
+            out.copy_(acc.transpose(0, 1))
+            return out
     kernels.gemm_batched_simt(x, weight, bias, out)
     return out
+
+
+_HAS_BMM_OUT_DTYPE: bool | None = None
+
+
+def _bmm(a: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor | None:
+    global _HAS_BMM_OUT_DTYPE
+    if out_dtype == a.dtype:
+        return torch.bmm(a, b)
+    if _HAS_BMM_OUT_DTYPE is False:
+        return None
+    try:
+        acc = torch.bmm(a, b, out_dtype=out_dtype)
+        _HAS_BMM_OUT_DTYPE = True
+        return acc
+    except (TypeError, RuntimeError):
+        _HAS_BMM_OUT_DTYPE = False
+        return None
 
 
 __all__ = ["linear", "batched_linear", "chosen_backend", "PendingSum", "resolve_backend", "EPILOGUE_NONE", "EPILOGUE_GELU", "EPILOGUE_RESIDUAL",

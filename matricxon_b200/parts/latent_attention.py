@@ -56,6 +56,30 @@ class LatentAttention(Mixer):
         self.value_up = fetch(p + s.value_up_name).view(s.num_heads, s.value_dim, s.latent_rank).contiguous()
         self.o_weight = fetch(p + s.output_name)
 
+    def _tiles(self, ctx):
+        """(tile list on the device or None, number of tiles) for the tensor-core kernel, built once per
+        step and head count. A fixed-size batch of decoding requests needs no list: tile i is sequence i."""
+        heads = self.spec.num_heads
+        if ctx.padded:
+            return None, ctx.n_seqs
+        key = ("latent_tiles", heads)
+        if key not in ctx.memo:
+            flat = kernels.latent_tile_list(ctx.host.q_lens, heads)
+            ctx.memo[key] = (torch.tensor(flat + [0, 0], dtype=torch.int32).to(ctx.device, non_blocking=True),
+                             len(flat) // 2)
+        return ctx.memo[key]
+
+    def _splits(self, ctx, n_tiles: int):
+        """Key splits: a block fills an SM's shared memory, so few tiles (decoding) leave SMs idle unless
+        each tile's keys are shared out; a split keeps at least four chunks of 32 keys."""
+        span = ctx.max_kv_len if self.spec.window is None else min(ctx.max_kv_len, self.spec.window)
+        blocks = n_tiles * (-(-self.spec.num_heads // 64) if ctx.padded else 1)
+        n_splits = max(1, min(ctx.sm_count // max(blocks, 1), (span // 32 + 1) // 4, 64))
+        if n_splits == 1:
+            return 1, None
+        return n_splits, ctx.scratch(kernels.attention_scratch_bytes(ctx.n_tokens, self.spec.num_heads,
+                                                                     self.spec.latent_rank, n_splits))
+
     def forward(self, h, residual, ctx, binding):
         s, rt = self.spec, self.runtime
         if binding.kv is None:
@@ -71,8 +95,15 @@ class LatentAttention(Mixer):
                                s.position.rotary_dim, rank, ctx.status)
         batched_linear(q_plain.view(n, heads, s.head_dim), self.key_up_t, None, q_lat[:, :, :rank])
         mixed = torch.empty((n, heads, rank), dtype=rt.dtype, device=h.device)
-        kernels.latent_attention(q_lat, binding.kv, ctx.groups[binding.group].block_tables, ctx.tok_seq,
-                                 ctx.positions, rank, s.window, s.scale, mixed, ctx.status)
+        tables = ctx.groups[binding.group].block_tables
+        if kernels.latent_attention_mma_supported(rt.dtype, rank, self.key_width):
+            tiles, n_tiles = self._tiles(ctx)
+            n_splits, scratch = self._splits(ctx, n_tiles)
+            kernels.latent_attention_mma(q_lat, binding.kv, tables, ctx.cu_q, ctx.context_lens, tiles, n_tiles, rank,
+                                         s.window, s.scale, mixed, ctx.status, n_splits=n_splits, scratch=scratch)
+        else:       # the 32-bit path, and sizes the tensor-core kernel does not take
+            kernels.latent_attention(q_lat, binding.kv, tables, ctx.tok_seq, ctx.positions, rank, s.window,
+                                     s.scale, mixed, ctx.status)
         attn = torch.empty((n, heads * s.value_dim), dtype=rt.dtype, device=h.device)
         batched_linear(mixed, self.value_up, None, attn.view(n, heads, s.value_dim))
         if residual is None:

@@ -69,9 +69,9 @@ class GatedLinearRecurrence(Mixer):
         kernels.causal_conv(branches, 0, self.conv_weight, self.conv_bias, binding.state, ctx.tok_seq, ctx.cu_q,
                             ctx.state_slots, u, None if u_act is u else u_act)
         gates = torch.empty((n, s.blocks, 2 * block), dtype=torch.float32, device=h.device)
-        batched_linear(u_act.view(n, s.blocks, block), self.gate_weight, self.gate_bias, gates)
+        batched_linear(u_act.view(n, s.blocks, block), self.gate_weight, None, gates)   # the scan adds the biases
         out = torch.empty((n, width), dtype=rt.dtype, device=h.device)
-        kernels.rglru_scan(branches, 0, width, u, gates, self.lam, s.decay, binding.state, ctx.cu_q,
+        kernels.rglru_scan(branches, 0, width, u, gates, self.gate_bias, self.lam, s.decay, binding.state, ctx.cu_q,
                            ctx.state_slots, ctx.n_seqs, block, out)
         if residual is None:
             return linear(out, self.o_weight, None, EPILOGUE_F32, backend=rt.gemm_backend)

@@ -111,7 +111,8 @@ def test_rms_norm_and_post_norm_sum(dtype, hidden, offset):
         assert torch.equal(act, stream.to(dtype))
 
 
-def _latent_case(dtype, n_heads, rank, rot, page_size, window, contexts, q_lens, seed, spike=None):
+def _latent_case(dtype, n_heads, rank, rot, page_size, window, contexts, q_lens, seed, spike=None,
+                 tensor_cores=False, n_splits=1, no_list=False):
     """Queries and a paged latent cache with shuffled pages; returns what the kernel gave and the plain sums.
     ``spike`` = (sequence, query offset, key position): that key's vector is made to dominate the query's
     scores if the query sees it."""
@@ -147,10 +148,23 @@ def _latent_case(dtype, n_heads, rank, rot, page_size, window, contexts, q_lens,
     out = torch.empty(q_all.shape[0], n_heads, rank, dtype=dtype, device=DEVICE)
     status = torch.zeros(1, dtype=torch.int32, device=DEVICE)
     scale = 2.0 / dk ** 0.5
-    kernels.latent_attention(q_all.to(dtype).to(DEVICE), cache.to(dtype).to(DEVICE), tables.to(DEVICE),
-                             torch.tensor(tok_seq, dtype=torch.int32, device=DEVICE),
-                             torch.tensor(positions, dtype=torch.int32, device=DEVICE), rank, window, scale, out,
-                             status)
+    if tensor_cores:
+        cu_q = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32, device=DEVICE)
+        flat = kernels.latent_tile_list(q_lens, n_heads)
+        tiles = None if no_list else torch.tensor(flat, dtype=torch.int32, device=DEVICE)
+        scratch = None
+        if n_splits > 1:
+            scratch = torch.full((kernels.attention_scratch_bytes(len(tok_seq), n_heads, rank, n_splits) // 4,),
+                                 float("nan"), device=DEVICE)
+        kernels.latent_attention_mma(q_all.to(dtype).to(DEVICE), cache.to(dtype).to(DEVICE), tables.to(DEVICE), cu_q,
+                                     torch.tensor(contexts, dtype=torch.int32, device=DEVICE), tiles,
+                                     len(q_lens) if no_list else len(flat) // 2, rank, window, scale, out, status,
+                                     n_splits=n_splits, scratch=scratch)
+    else:
+        kernels.latent_attention(q_all.to(dtype).to(DEVICE), cache.to(dtype).to(DEVICE), tables.to(DEVICE),
+                                 torch.tensor(tok_seq, dtype=torch.int32, device=DEVICE),
+                                 torch.tensor(positions, dtype=torch.int32, device=DEVICE), rank, window, scale,
+                                 out, status)
     assert int(status.item()) == 0
     want = torch.empty(q_all.shape[0], n_heads, rank, dtype=torch.float64)
     for row, (s, p) in enumerate(zip(tok_seq, positions)):
@@ -169,6 +183,37 @@ def test_latent_attention_kernel(dtype, n_heads, rank, rot, page_size, window):
                                 q_lens=[45, 1, 30, 2], seed=rank)
     tol = 2e-5 if dtype == torch.float32 else 0.03
     assert torch.allclose(got, want, rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("n_splits", [1, 3])
+@pytest.mark.parametrize("n_heads, rank, rot, page_size, window", [
+    (3, 64, 16, 16, 20), (9, 160, 16, 8, 33), (1, 32, 0, 16, None), (16, 512, 64, 32, 64), (70, 96, 32, 16, 50)])
+def test_latent_attention_on_tensor_cores(n_heads, rank, rot, page_size, window, n_splits):
+    """Prompt portions and single tokens in one launch; tiles that straddle tokens (heads no divisor of 64),
+    more heads than a tile has rows, keys shared out between blocks."""
+    got, want, _ = _latent_case(torch.bfloat16, n_heads, rank, rot, page_size, window, contexts=[0, 70, 5, 129],
+                                q_lens=[45, 1, 30, 2], seed=rank, tensor_cores=True, n_splits=n_splits)
+    assert torch.allclose(got, want, rtol=0.03, atol=0.03)
+    # a fixed-size batch of decoding requests: no tile list, one sequence of them brings nothing
+    got, want, _ = _latent_case(torch.bfloat16, n_heads, rank, rot, page_size, window, contexts=[3, 70, 0, 129],
+                                q_lens=[1, 1, 1, 1], seed=rank + 1, tensor_cores=True, n_splits=n_splits,
+                                no_list=True)
+    assert torch.allclose(got, want, rtol=0.03, atol=0.03)
+
+
+@pytest.mark.parametrize("decode", [False, True])
+@pytest.mark.parametrize("distance, seen", [(23, True), (24, False), (16, True), (1, True), (0, True)])
+def test_latent_attention_on_tensor_cores_window_edge(decode, distance, seen):
+    context, q_len = (90, 1) if decode else (40, 51)
+    position = context + q_len - 1
+    got, want, vectors = _latent_case(torch.bfloat16, 2, 32, 16, 16, 24, contexts=[3, context], q_lens=[4, q_len],
+                                      seed=distance, spike=(1, q_len - 1, position - distance), tensor_cores=True,
+                                      n_splits=2 if decode else 1)
+    assert torch.allclose(got, want, rtol=0.03, atol=0.03)
+    row = got.shape[0] - 1
+    key = vectors[1][position - distance][:32].double()
+    cosine = torch.dot(got[row, 0], key) / (got[row, 0].norm() * key.norm())
+    assert (cosine.item() > 0.95) == seen
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
