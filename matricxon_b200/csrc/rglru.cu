@@ -17,6 +17,11 @@
 //   then stores S and the last taps-1 inputs. Everything is float; only `out` is rounded.
 //   sqrt(1 - a^2) is taken as sqrt(-expm1(2 log a)), which keeps its digits when a is close to one.
 // A sequence that brings no token in this step (a padding row of a fixed-size batch) is skipped.
+// mx_rglru_scan_chunked does the same for long portions in three launches, since the recurrence is linear
+// in S: per chunk of at most 32 tokens and channel, the chunk's map S -> A S + B (A the product of its
+// a, B its own contribution); per sequence and channel, the chunks' start states in order, from and to
+// the request's state; per chunk and channel again, the tokens from the chunk's start state. A token's
+// result is the same sequence of float operations whatever else the step holds.
 #include <math.h>
 
 #include "common.cuh"
@@ -88,7 +93,112 @@ __global__ void rglru_scan_kernel(const float* __restrict__ xy, int ld, int x_co
     }
 }
 
+struct GateTerms { float a, b; };
+
+__device__ __forceinline__ GateTerms gate_terms(const float* g, int block_width, float bias_r, float bias_i,
+                                                float rate, float u) {
+    const float r = 1.0f / (1.0f + expf(-(g[0] + bias_r)));
+    const float i = 1.0f / (1.0f + expf(-(g[block_width] + bias_i)));
+    const float log_a = rate * r;
+    GateTerms t;
+    t.a = expf(log_a);
+    t.b = sqrtf(-expm1f(2.0f * log_a)) * (i * u);
+    return t;
+}
+
+struct ChunkScan {
+    const float* xy; const float* u; const float* gates; const float* gate_bias; const float* lambda;
+    float* state; const int* cu_q; const int* state_slots;
+    const int* chunks;        // [n_chunks][2]: (sequence, first token of the chunk within the sequence's portion)
+    const int* seq_chunk0;    // [n_seqs + 1]: index of each sequence's first chunk
+    float* chunk_a; float* chunk_b; float* chunk_start;   // [n_chunks][width]
+    int ld, x_col, y_col, width, block_width, taps, chunk_tokens;
+    float decay;
+};
+
+template <typename T, int PHASE>   // 0: the chunks' maps; 2: the tokens from the chunks' start states
+__global__ void rglru_chunk_kernel(const ChunkScan p, T* __restrict__ out) {
+    const int chunk = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= p.width) return;
+    const int seq = p.chunks[2 * chunk], first = p.chunks[2 * chunk + 1];
+    const int t0 = p.cu_q[seq] + first;
+    const int n = min(p.chunk_tokens, p.cu_q[seq + 1] - t0);
+    const int b = c / p.block_width, j = c - b * p.block_width;
+    const size_t gate_col = (size_t)b * 2 * p.block_width + j;
+    const float bias_r = p.gate_bias ? p.gate_bias[gate_col] : 0.f;
+    const float bias_i = p.gate_bias ? p.gate_bias[gate_col + p.block_width] : 0.f;
+    const float lam = p.lambda[c];
+    const float rate = -p.decay * (lam > 20.f ? lam : log1pf(expf(lam)));
+    if (PHASE == 0) {
+        float a_all = 1.f, b_all = 0.f;
+        for (int k = 0; k < n; ++k) {
+            const size_t t = (size_t)(t0 + k);
+            const GateTerms g = gate_terms(p.gates + t * 2 * p.width + gate_col, p.block_width, bias_r, bias_i, rate,
+                                           p.u[t * p.width + c]);
+            a_all *= g.a;
+            b_all = fmaf(g.a, b_all, g.b);
+        }
+        p.chunk_a[(size_t)chunk * p.width + c] = a_all;
+        p.chunk_b[(size_t)chunk * p.width + c] = b_all;
+    } else {
+        float s = p.chunk_start[(size_t)chunk * p.width + c];
+        for (int k = 0; k < n; ++k) {
+            const size_t t = (size_t)(t0 + k);
+            const GateTerms g = gate_terms(p.gates + t * 2 * p.width + gate_col, p.block_width, bias_r, bias_i, rate,
+                                           p.u[t * p.width + c]);
+            s = fmaf(g.a, s, g.b);
+            out[t * p.width + c] = from_float<T>(s * gelu_tanh(p.xy[t * p.ld + p.y_col + c]));
+        }
+    }
+}
+
+__global__ void rglru_carry_kernel(const ChunkScan p) {
+    const int seq = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= p.width) return;
+    const int t0 = p.cu_q[seq], n = p.cu_q[seq + 1] - t0;
+    if (n <= 0) return;
+    float* st = p.state + (size_t)p.state_slots[seq] * p.taps * p.width;
+    float s = st[(size_t)(p.taps - 1) * p.width + c];
+    for (int chunk = p.seq_chunk0[seq]; chunk < p.seq_chunk0[seq + 1]; ++chunk) {
+        p.chunk_start[(size_t)chunk * p.width + c] = s;
+        s = fmaf(p.chunk_a[(size_t)chunk * p.width + c], s, p.chunk_b[(size_t)chunk * p.width + c]);
+    }
+    st[(size_t)(p.taps - 1) * p.width + c] = s;
+    for (int r = 0; r < p.taps - 1; ++r) {
+        const int idx = n - (p.taps - 1) + r;
+        st[(size_t)r * p.width + c] = idx >= 0 ? p.xy[(size_t)(t0 + idx) * p.ld + p.x_col + c]
+                                               : st[(size_t)(idx + p.taps - 1) * p.width + c];
+    }
+}
+
 }  // namespace
+
+// Note on equality with mx_rglru_scan: inside a chunk the state is advanced by the same fmaf chain; across
+// chunks the start state is A S + B instead of that chain, which differs by float rounding only.
+extern "C" int mx_rglru_scan_chunked(const float* xy, int ld, int x_col, int y_col, const float* u,
+                                     const float* gates, const float* gate_bias, const float* lambda, float decay,
+                                     float* state, const int* cu_q, const int* state_slots, const int* chunks,
+                                     const int* seq_chunk0, int n_chunks, int chunk_tokens, float* scratch,
+                                     void* out, int out_dtype, int n_seqs, int width, int block_width, int taps,
+                                     cudaStream_t stream) {
+    if (n_seqs <= 0 || n_chunks <= 0) return MX_OK;
+    if (block_width <= 0 || width % block_width) MX_REFUSE("recurrence: width %d in blocks of %d", width, block_width);
+    ChunkScan p;
+    p.xy = xy; p.u = u; p.gates = gates; p.gate_bias = gate_bias; p.lambda = lambda; p.state = state;
+    p.cu_q = cu_q; p.state_slots = state_slots; p.chunks = chunks; p.seq_chunk0 = seq_chunk0;
+    p.chunk_a = scratch; p.chunk_b = scratch + (size_t)n_chunks * width; p.chunk_start = scratch + 2 * (size_t)n_chunks * width;
+    p.ld = ld; p.x_col = x_col; p.y_col = y_col; p.width = width; p.block_width = block_width; p.taps = taps;
+    p.chunk_tokens = chunk_tokens; p.decay = decay;
+    const int threads = 128;
+    const dim3 per_chunk(n_chunks, (width + threads - 1) / threads), per_seq(n_seqs, (width + threads - 1) / threads);
+    rglru_chunk_kernel<float, 0><<<per_chunk, threads, 0, stream>>>(p, (float*)nullptr);
+    rglru_carry_kernel<<<per_seq, threads, 0, stream>>>(p);
+    if (out_dtype == MX_DTYPE_F32) rglru_chunk_kernel<float, 2><<<per_chunk, threads, 0, stream>>>(p, (float*)out);
+    else rglru_chunk_kernel<__nv_bfloat16, 2><<<per_chunk, threads, 0, stream>>>(p, (__nv_bfloat16*)out);
+    return mx_launch_status();
+}
 
 extern "C" int mx_causal_conv(const float* xy, int ld, int x_col, const float* conv_weight,
                               const float* conv_bias, const float* state, const int* tok_seq, const int* cu_q,

@@ -62,6 +62,49 @@ __global__ void rmsnorm_sum_kernel(float* x, const float* __restrict__ acc, floa
     }
 }
 
+// The same for rows whose length is a multiple of 4: float4 accesses, up to RMS_VEC float4 a thread in registers.
+constexpr int RMS_VEC = 4;
+
+template <typename TAct>
+__global__ void rmsnorm_sum_vec_kernel(float* x, const float* __restrict__ acc, float alpha,
+                                       const float* __restrict__ weight, float offset, TAct* act, int hidden,
+                                       float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    float4* xr = reinterpret_cast<float4*>(x + (size_t)r * hidden);
+    const float4* ar = reinterpret_cast<const float4*>(acc + (size_t)r * hidden);
+    const float4* wr = reinterpret_cast<const float4*>(weight);
+    const int vecs = hidden >> 2;
+    float4 kept[RMS_VEC];
+    float s = 0.f;
+#pragma unroll
+    for (int n = 0; n < RMS_VEC; ++n) {
+        const int i = threadIdx.x + n * blockDim.x;
+        if (i < vecs) {
+            const float4 a = xr[i], b = ar[i];
+            kept[n] = make_float4(fmaf(alpha, a.x, b.x), fmaf(alpha, a.y, b.y), fmaf(alpha, a.z, b.z), fmaf(alpha, a.w, b.w));
+            s = fmaf(kept[n].x, kept[n].x, s); s = fmaf(kept[n].y, kept[n].y, s);
+            s = fmaf(kept[n].z, kept[n].z, s); s = fmaf(kept[n].w, kept[n].w, s);
+        }
+    }
+    const float inv = 1.0f / sqrtf(block_sum(s, scratch) / (float)hidden + eps);
+#pragma unroll
+    for (int n = 0; n < RMS_VEC; ++n) {
+        const int i = threadIdx.x + n * blockDim.x;
+        if (i < vecs) {
+            const float4 w = wr[i];
+            const float4 v = make_float4(kept[n].x * inv * (offset + w.x), kept[n].y * inv * (offset + w.y),
+                                         kept[n].z * inv * (offset + w.z), kept[n].w * inv * (offset + w.w));
+            xr[i] = v;
+            if (act) {
+                TAct* dst = act + (size_t)r * hidden + 4 * i;
+                dst[0] = from_float<TAct>(v.x); dst[1] = from_float<TAct>(v.y);
+                dst[2] = from_float<TAct>(v.z); dst[3] = from_float<TAct>(v.w);
+            }
+        }
+    }
+}
+
 __global__ void cast_rows_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ out, long long count) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < count) out[i] = __float2bfloat16_rn(x[i]);
@@ -90,6 +133,20 @@ extern "C" int mx_rmsnorm_sum(float* x, const float* acc, float alpha, const flo
     if (n_rows <= 0) return MX_OK;
     if (hidden <= 0) MX_REFUSE("rmsnorm: hidden must be positive, got %d", hidden);
     if (acc == nullptr) MX_REFUSE("rmsnorm with sum: no accumulator");
+    if (hidden % 4 == 0 && hidden <= 4 * RMS_VEC * 1024) {
+        // a thread per float4 where the row allows it (few rows: the row's latency is all there is); long rows
+        // take up to RMS_VEC float4 a thread
+        int vthreads = ((hidden / 4 + RMS_VEC - 1) / RMS_VEC + 31) / 32 * 32;
+        if (n_rows <= 64) vthreads = (hidden / 4 + 31) / 32 * 32;
+        vthreads = vthreads > 1024 ? 1024 : vthreads;
+        if (act == nullptr || act_dtype == MX_DTYPE_F32)
+            rmsnorm_sum_vec_kernel<float><<<n_rows, vthreads, 0, stream>>>(x, acc, alpha, weight, offset, (float*)act,
+                                                                         hidden, eps);
+        else
+            rmsnorm_sum_vec_kernel<__nv_bfloat16><<<n_rows, vthreads, 0, stream>>>(
+                x, acc, alpha, weight, offset, (__nv_bfloat16*)act, hidden, eps);
+        return mx_launch_status();
+    }
     const int threads = threads_for(hidden);
     if (act == nullptr || act_dtype == MX_DTYPE_F32)
         rmsnorm_sum_kernel<float><<<n_rows, threads, 0, stream>>>(x, acc, alpha, weight, offset, (float*)act,

@@ -574,6 +574,29 @@ def gemm_batched_simt(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | Non
     _launched()
 
 
+def batched_skinny_supported(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and a.shape[0] <= 16 and a.shape[2] % 8 == 0 and a.stride(2) == 1
+            and a.stride(0) % 8 == 0 and a.stride(1) % 8 == 0 and w.is_contiguous() and out.stride(2) == 1
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_batched_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """``gemm_batched_simt`` without a bias for at most 16 rows of bfloat16: a warp per output column, the
+    weights read once with 16-byte loads."""
+    _need(a, "a", torch.bfloat16, contiguous=False)
+    _need(w, "w", torch.bfloat16)
+    _need(out, "out", contiguous=False)
+    m, batch, k = a.shape
+    n = w.shape[1]
+    assert tuple(w.shape) == (batch, n, k) and tuple(out.shape) == (m, batch, n), (a.shape, w.shape, out.shape)
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelLibraryError(f"a batched product writes bfloat16 or float32, not {out.dtype}")
+    check(library().mx_gemm_batched_skinny(_ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype), m, n, k, a.stride(0),
+                                           w.stride(1), out.stride(0), batch, a.stride(1), w.stride(0),
+                                           out.stride(1), _stream()), "gemm_batched_skinny")
+    _launched()
+
+
 # ---------------------------------------------------------------------- latent attention
 def latent_prepare(proj: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor, amplitude: float,
                    latent_weight: torch.Tensor, eps: float, slots: torch.Tensor | None,
@@ -779,3 +802,46 @@ def rglru_scan(xy: torch.Tensor, x_col: int, y_col: int, u: torch.Tensor, gates:
                                   dtype_code(out.dtype), n_seqs, width, block_width, taps, _stream()),
           "rglru_scan")
     _launched()
+
+
+SCAN_CHUNK = 32     # tokens per chunk of the three-launch recurrence
+
+
+def scan_chunk_lists(q_lens: list[int]) -> tuple[list[int], list[int]]:
+    """For ``rglru_scan_chunked``: (sequence, first token) of every chunk of ``SCAN_CHUNK`` tokens,
+    flattened, sequence by sequence, and the index of each sequence's first chunk (one more entry than
+    sequences)."""
+    chunks: list[int] = []
+    first = [0]
+    for seq, q_len in enumerate(q_lens):
+        for start in range(0, q_len, SCAN_CHUNK):
+            chunks.extend((seq, start))
+        first.append(len(chunks) // 2)
+    return chunks, first
+
+
+def rglru_scan_chunked(xy: torch.Tensor, x_col: int, y_col: int, u: torch.Tensor, gates: torch.Tensor,
+                       gate_bias: torch.Tensor | None, lam: torch.Tensor, decay: float, state: torch.Tensor,
+                       cu_q: torch.Tensor, state_slots: torch.Tensor, n_seqs: int, block_width: int,
+                       chunks: torch.Tensor, seq_chunk0: torch.Tensor, n_chunks: int, scratch: torch.Tensor,
+                       out: torch.Tensor) -> None:
+    """``rglru_scan`` for long portions: chunk maps, the chunks' start states in order, then the tokens
+    (three launches, every token of every chunk in parallel). ``chunks`` / ``seq_chunk0`` are
+    ``scan_chunk_lists`` on the device; ``scratch`` is float32 with 3 * n_chunks * width elements."""
+    for name, tensor in (("xy", xy), ("u", u), ("gates", gates), ("lambda", lam), ("state", state),
+                         ("scratch", scratch)):
+        _need(tensor, name, torch.float32)
+    _need(chunks, "chunks", torch.int32)
+    _need(seq_chunk0, "seq_chunk0", torch.int32)
+    _need(out, "out")
+    n, width = u.shape
+    taps = state.shape[1]
+    assert gates.numel() == n * 2 * width and tuple(out.shape) == (n, width) and lam.numel() == width
+    assert chunks.numel() >= 2 * n_chunks and seq_chunk0.numel() >= n_seqs + 1
+    assert scratch.numel() >= 3 * n_chunks * width
+    check(library().mx_rglru_scan_chunked(_ptr(xy), xy.stride(0), x_col, y_col, _ptr(u), _ptr(gates),
+                                          _ptr(gate_bias), _ptr(lam), float(decay), _ptr(state), _ptr(cu_q),
+                                          _ptr(state_slots), _ptr(chunks), _ptr(seq_chunk0), n_chunks, SCAN_CHUNK,
+                                          _ptr(scratch), _ptr(out), dtype_code(out.dtype), n_seqs, width,
+                                          block_width, taps, _stream()), "rglru_scan_chunked")
+    _launched(3)

@@ -57,6 +57,8 @@ _SIGNATURES: dict[str, tuple[list, object]] = {
     "mx_clamped_glu": ([P, I, P, I, I, I, F, F, F, P], I),
     "mx_causal_conv": ([P, I, I, P, P, P, P, P, P, P, P, I, I, I, I, P], I),
     "mx_rglru_scan": ([P, I, I, I, P, P, P, P, F, P, P, P, P, I, I, I, I, I, P], I),
+    "mx_rglru_scan_chunked": ([P, I, I, I, P, P, P, P, F, P, P, P, P, P, I, I, P, P, I, I, I, I, I, P], I),
+    "mx_gemm_batched_skinny": ([P, P, P, I, I, I, I, I, I, I, I, L, L, L, P], I),
     "mx_gemm_batched_simt": ([P, P, I, P, P, I, I, I, I, I, I, I, I, L, L, L, L, I, P], I),
 }
 

@@ -189,6 +189,9 @@ def batched_linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | N
     side in a row); weight [B, N, K] in the dtype of x; bias float32 [B, N]; out in the dtype of x or float32."""
     if x.shape[0] == 0:
         return out
+    if bias is None and kernels.batched_skinny_supported(x, weight, out):
+        kernels.gemm_batched_skinny(x, weight, out)         # a decode step's few rows
+        return out
     if x.dtype == torch.bfloat16 and bias is None and x.shape[0] > 32:
         # many rows: the library's strided batched product (float accumulator kept for a float result),
         # then one strided copy into the caller's interleaved layout

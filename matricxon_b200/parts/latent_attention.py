@@ -71,10 +71,10 @@ class LatentAttention(Mixer):
 
     def _splits(self, ctx, n_tiles: int):
         """Key splits: a block fills an SM's shared memory, so few tiles (decoding) leave SMs idle unless
-        each tile's keys are shared out; a split keeps at least four chunks of 32 keys."""
+        each tile's keys are shared out; a split keeps at least eight chunks of 32 keys."""
         span = ctx.max_kv_len if self.spec.window is None else min(ctx.max_kv_len, self.spec.window)
         blocks = n_tiles * (-(-self.spec.num_heads // 64) if ctx.padded else 1)
-        n_splits = max(1, min(ctx.sm_count // max(blocks, 1), (span // 32 + 1) // 4, 64))
+        n_splits = max(1, min(ctx.sm_count // max(blocks, 1), (span // 32 + 1) // 8, 64))
         if n_splits == 1:
             return 1, None
         return n_splits, ctx.scratch(kernels.attention_scratch_bytes(ctx.n_tokens, self.spec.num_heads,

@@ -71,8 +71,22 @@ class GatedLinearRecurrence(Mixer):
         gates = torch.empty((n, s.blocks, 2 * block), dtype=torch.float32, device=h.device)
         batched_linear(u_act.view(n, s.blocks, block), self.gate_weight, None, gates)   # the scan adds the biases
         out = torch.empty((n, width), dtype=rt.dtype, device=h.device)
-        kernels.rglru_scan(branches, 0, width, u, gates, self.gate_bias, self.lam, s.decay, binding.state, ctx.cu_q,
-                           ctx.state_slots, ctx.n_seqs, block, out)
+        if not ctx.padded and max(ctx.host.q_lens) > 2 * kernels.SCAN_CHUNK:
+            # long portions: the recurrence in chunks (a token-by-token walk of thousands of tokens would
+            # leave the GPU to a few warps)
+            key = "scan_chunks"
+            if key not in ctx.memo:
+                chunks, first = kernels.scan_chunk_lists(ctx.host.q_lens)
+                both = torch.tensor(chunks + first, dtype=torch.int32).to(h.device, non_blocking=True)
+                ctx.memo[key] = (both[:len(chunks)], both[len(chunks):], len(chunks) // 2)
+            chunks, first, n_chunks = ctx.memo[key]
+            scratch = torch.empty(3 * n_chunks * width, dtype=torch.float32, device=h.device)
+            kernels.rglru_scan_chunked(branches, 0, width, u, gates, self.gate_bias, self.lam, s.decay,
+                                       binding.state, ctx.cu_q, ctx.state_slots, ctx.n_seqs, block, chunks, first,
+                                       n_chunks, scratch, out)
+        else:
+            kernels.rglru_scan(branches, 0, width, u, gates, self.gate_bias, self.lam, s.decay, binding.state,
+                               ctx.cu_q, ctx.state_slots, ctx.n_seqs, block, out)
         if residual is None:
             return linear(out, self.o_weight, None, EPILOGUE_F32, backend=rt.gemm_backend)
         return linear(out, self.o_weight, None, EPILOGUE_RESIDUAL, residual=residual, out=residual,

@@ -90,7 +90,7 @@ class Run:
 
 # ---------------------------------------------------------------------- kernels alone
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("hidden, offset", [(96, 1.0), (1000, 0.0), (9000, 1.0)])
+@pytest.mark.parametrize("hidden, offset", [(96, 1.0), (1002, 0.0), (9000, 1.0), (18002, 1.0)])
 def test_rms_norm_and_post_norm_sum(dtype, hidden, offset):
     torch.manual_seed(hidden)
     x = torch.randn(7, hidden, device=DEVICE) * 3
