@@ -8,7 +8,7 @@
 // sum_j p_j c_j; the per-head value expansion Uv_h follows as another batched product. So this is
 // attention with one key/value head whose value is the first `rank` elements of its key.
 //
-// mx_latent_prepare (one block per token) reads the float result of the fused query / down
+// mx_latent_prepare (per token one block for the cache vector and one per four query heads) reads the float result of the fused query / down
 // projection, [q heads (plain | rot) | latent | shared rot], and writes
 //   q_plain [tokens][heads * dim]          (activation dtype: the batched product's operand)
 //   q_lat   [tokens][heads][Dk]            the rotated query part at offset rank
@@ -30,6 +30,7 @@ constexpr int LAT_THREADS = 128;
 constexpr int LAT_WARPS = LAT_THREADS / 32;
 constexpr int LAT_HEADS = 8;      // heads per block at most
 constexpr int LAT_KEYS = 32;
+constexpr int LAT_PREP_HEADS = 4;  // query heads per block of the preparing kernel
 
 template <typename T>
 __global__ void __launch_bounds__(LAT_THREADS)
@@ -52,22 +53,27 @@ latent_prepare_kernel(const float* __restrict__ qd, int ld, const int* __restric
     __syncthreads();
     const float* row = qd + (size_t)t * ld;
     const int qw = dim + rot;
-    // plain query parts, head by head
-    for (int item = threadIdx.x; item < n_heads * dim; item += blockDim.x) {
-        const int h = item / dim, d = item - h * dim;
-        q_plain[(size_t)t * n_heads * dim + item] = from_float<T>(row[(size_t)h * qw + d]);
+    if (blockIdx.y > 0) {
+        // blocks 1 .. of a token: LAT_PREP_HEADS query heads each
+        const int h0 = (blockIdx.y - 1) * LAT_PREP_HEADS, h1 = min(n_heads, h0 + LAT_PREP_HEADS);
+        for (int h = h0; h < h1; ++h) {
+            const float* src = row + (size_t)h * qw;
+            // the plain part, as the batched product's operand
+            for (int d = threadIdx.x; d < dim; d += blockDim.x)
+                q_plain[((size_t)t * n_heads + h) * dim + d] = from_float<T>(src[d]);
+            // the rotated part, to the tail of the head's latent-space query
+            src += dim;
+            for (int d = threadIdx.x; d < rot; d += blockDim.x) {
+                float v;
+                if (d < half) v = src[d] * cs[d] - src[d + half] * cs[half + d];
+                else if (d < rot_dims) v = src[d] * cs[d - half] + src[d - half] * cs[d];
+                else v = src[d];
+                q_lat[((size_t)t * n_heads + h) * dk + rank + d] = from_float<T>(v);
+            }
+        }
+        return;
     }
-    // rotated query parts, to the tail of each head's latent-space query
-    for (int item = threadIdx.x; item < n_heads * rot; item += blockDim.x) {
-        const int h = item / rot, d = item - h * rot;
-        const float* src = row + (size_t)h * qw + dim;
-        float v;
-        if (d < half) v = src[d] * cs[d] - src[d + half] * cs[half + d];
-        else if (d < rot_dims) v = src[d] * cs[d - half] + src[d - half] * cs[d];
-        else v = src[d];
-        q_lat[((size_t)t * n_heads + h) * dk + rank + d] = from_float<T>(v);
-    }
-    // the token's cache vector
+    // block 0 of a token: its cache vector
     const long long slot = slots ? slots[t] : -1;
     const float* lat = row + (size_t)n_heads * qw;
     float s = 0.f;
@@ -237,12 +243,13 @@ extern "C" int mx_latent_prepare(const float* qd, int ld, const int* positions, 
     if (ld < n_heads * (dim + rot) + rank + rot) MX_REFUSE("latent attention: projection rows are too short");
     const size_t smem = (size_t)(rot_dims > 0 ? rot_dims : 1) * sizeof(float);
     const long long n_slots = n_pages * page_size;
+    const dim3 grid(n_tokens, 1 + (n_heads + LAT_PREP_HEADS - 1) / LAT_PREP_HEADS);
     if (dtype == MX_DTYPE_F32)
-        latent_prepare_kernel<float><<<n_tokens, LAT_THREADS, smem, stream>>>(
+        latent_prepare_kernel<float><<<grid, LAT_THREADS, smem, stream>>>(
             qd, ld, positions, freq, amplitude, latent_weight, eps, cache ? slots : nullptr, (float*)cache, n_slots,
             (float*)q_plain, (float*)q_lat, n_heads, dim, rot, rot_dims, rank, status);
     else
-        latent_prepare_kernel<__nv_bfloat16><<<n_tokens, LAT_THREADS, smem, stream>>>(
+        latent_prepare_kernel<__nv_bfloat16><<<grid, LAT_THREADS, smem, stream>>>(
             qd, ld, positions, freq, amplitude, latent_weight, eps, cache ? slots : nullptr, (__nv_bfloat16*)cache,
             n_slots, (__nv_bfloat16*)q_plain, (__nv_bfloat16*)q_lat, n_heads, dim, rot, rot_dims, rank, status);
     return mx_launch_status();

@@ -116,27 +116,25 @@ latent_attention_mma_kernel(const LatentMmaParams p) {
     }
 
     const int* bt = p.block_tables + (size_t)seq * p.bt_stride;
+    // eight threads a key: one look at the block table per thread and chunk, then the key's vectors in turn
     auto issue = [&](int chunk, int stage) {
-        __nv_bfloat16* dst = k_s + stage * LT_KEYS * ks;
-        const int c0 = chunk * LT_KEYS;
-        for (int item = tid; item < LT_KEYS * vecs; item += LT_THREADS) {
-            const int j = item / vecs, v = item - j * vecs;
-            const int kpos = c0 + j;
-            __nv_bfloat16* d = dst + j * ks + v * 8;
-            long long page = -1;
-            int lp = 0;
-            if (kpos >= lo_tile && kpos <= hi) {
-                lp = kpos / p.page_size;
-                page = lp < p.bt_stride ? bt[lp] : -1;
-                if (page < 0 || page >= p.n_pages) {
-                    if (v == 0) atomicOr(p.status, MX_STATUS_BAD_PAGE);
-                    page = -1;
-                }
+        const int j = tid >> 3, sub = tid & 7;
+        const int kpos = chunk * LT_KEYS + j;
+        __nv_bfloat16* d = k_s + (stage * LT_KEYS + j) * ks;
+        const __nv_bfloat16* src = nullptr;
+        if (kpos >= lo_tile && kpos <= hi) {
+            const int lp = kpos / p.page_size;
+            const long long page = lp < p.bt_stride ? bt[lp] : -1;
+            if (page < 0 || page >= p.n_pages) {
+                if (sub == 0) atomicOr(p.status, MX_STATUS_BAD_PAGE);
+            } else {
+                src = p.cache + ((size_t)page * p.page_size + (kpos - lp * p.page_size)) * dk;
             }
-            if (page >= 0)
-                cp_async16(lt_smem(d), p.cache + ((size_t)page * p.page_size + (kpos - lp * p.page_size)) * dk + v * 8);
-            else
-                *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+        }
+        if (src) {
+            for (int v = sub; v < vecs; v += 8) cp_async16(lt_smem(d + v * 8), src + v * 8);
+        } else {
+            for (int v = sub; v < vecs; v += 8) *reinterpret_cast<uint4*>(d + v * 8) = make_uint4(0, 0, 0, 0);
         }
     };
 
@@ -157,6 +155,7 @@ latent_attention_mma_kernel(const LatentMmaParams p) {
         for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     const int nvp = rank >> 5;                       // pairs of value tiles a warp owns (rank / 2 columns)
+    const bool rg_live = rg * 16 < rows_here;        // a row group beyond the tile's rows only helps with the copies
     const int col_base = half * (rank >> 1);
 
     if (c_begin < c_end) issue(c_begin, 0);
@@ -174,16 +173,39 @@ latent_attention_mma_kernel(const LatentMmaParams p) {
         for (int n = 0; n < 2; ++n)
 #pragma unroll
             for (int e = 0; e < 4; ++e) s[n][e] = 0.f;
-        {
+        if (rg_live) {
+            // two chains of accumulators (even and odd steps of the contraction), added at the end: an MMA
+            // need not wait for the one before it
+            float s2[2][4];
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s2[n][e] = 0.f;
             const unsigned a_addr = lt_smem(q_s + (rg * 16 + (lane & 15)) * ks + (lane >> 4) * 8);
             const unsigned b_addr = lt_smem(kc + (half * 16 + (lane >> 4) * 8 + (lane & 7)) * ks + ((lane >> 3) & 1) * 8);
-            for (int kk = 0; kk < dk; kk += 16) {
+            int kk = 0;
+            for (; kk + 32 <= dk; kk += 32) {
+                unsigned a0, a1, a2, a3, b0, b1, b2, b3, c0, c1, c2, c3, d0, d1, d2, d3;
+                ldsm_x4(a_addr + kk * 2, a0, a1, a2, a3);
+                ldsm_x4(b_addr + kk * 2, b0, b1, b2, b3);
+                ldsm_x4(a_addr + kk * 2 + 32, c0, c1, c2, c3);
+                ldsm_x4(b_addr + kk * 2 + 32, d0, d1, d2, d3);
+                lt_mma(s[0], a0, a1, a2, a3, b0, b1);
+                lt_mma(s[1], a0, a1, a2, a3, b2, b3);
+                lt_mma(s2[0], c0, c1, c2, c3, d0, d1);
+                lt_mma(s2[1], c0, c1, c2, c3, d2, d3);
+            }
+            if (kk < dk) {
                 unsigned a0, a1, a2, a3, b0, b1, b2, b3;
                 ldsm_x4(a_addr + kk * 2, a0, a1, a2, a3);
                 ldsm_x4(b_addr + kk * 2, b0, b1, b2, b3);
                 lt_mma(s[0], a0, a1, a2, a3, b0, b1);
                 lt_mma(s[1], a0, a1, a2, a3, b2, b3);
             }
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[n][e] += s2[n][e];
         }
         const int key0 = chunk * LT_KEYS + half * 16 + 2 * tq;
         float mx[2] = {-INFINITY, -INFINITY};
@@ -224,12 +246,12 @@ latent_attention_mma_kernel(const LatentMmaParams p) {
         }
         __syncthreads();
         // ---- O = alpha O + P V for this warp's columns
+        if (rg_live) {
 #pragma unroll
-        for (int n = 0; n < NVT; ++n) {
-            o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
-            o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
-        }
-        {
+            for (int n = 0; n < NVT; ++n) {
+                o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
+                o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+            }
             const unsigned pa_addr = lt_smem(p_s + (rg * 16 + (lane & 15)) * LT_PSTRIDE + (lane >> 4) * 8);
             unsigned pa[2][4];
             ldsm_x4(pa_addr, pa[0][0], pa[0][1], pa[0][2], pa[0][3]);
