@@ -96,6 +96,9 @@ __global__ void clamped_glu_kernel(const T* __restrict__ gu, int ld, T* __restri
 // eight neighbouring columns a thread, 16-byte accesses (bfloat16 rows whose width and stride are multiples of 8)
 __global__ void clamped_glu_vec_kernel(const __nv_bfloat16* __restrict__ gu, int ld, __nv_bfloat16* __restrict__ out,
                                        int ff, float limit, float slope, float shift, long long groups) {
+    pdl_trigger();
+    pdl_wait();
+    gu = after_wait(gu);
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= groups) return;
     const int per_row = ff >> 3;
@@ -166,8 +169,8 @@ extern "C" int mx_clamped_glu(const void* gu, int ld, void* out, int dtype, int 
     const unsigned blocks = (unsigned)((count + 255) / 256);
     if (dtype == MX_DTYPE_BF16 && ff % 8 == 0 && ld % 8 == 0 && ((uintptr_t)gu % 16 == 0) && ((uintptr_t)out % 16 == 0)) {
         const long long groups = count >> 3;
-        clamped_glu_vec_kernel<<<(unsigned)((groups + 255) / 256), 256, 0, stream>>>(
-            (const __nv_bfloat16*)gu, ld, (__nv_bfloat16*)out, ff, limit, slope, shift, groups);
+        mx_launch_chained(clamped_glu_vec_kernel, dim3((unsigned)((groups + 255) / 256)), dim3(256), 0, stream,
+                          (const __nv_bfloat16*)gu, ld, (__nv_bfloat16*)out, ff, limit, slope, shift, groups);
         return mx_launch_status();
     }
     if (dtype == MX_DTYPE_F32)

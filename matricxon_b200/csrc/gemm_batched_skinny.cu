@@ -5,7 +5,7 @@
 // elements 8l .. 8l+7 of every block of 256), every row of A against it, and the lanes' partial sums are
 // added by shuffles in a fixed order, so a row's result does not depend on the other rows. The operands
 // of the batch members may interleave (heads side by side in a row): rows are lda / ldo apart, members
-// a_batch / w_batch / o_batch apart. K must be a multiple of 8 and every row 16-byte aligned.
+// a_batch / w_batch / o_batch apart. Takes part in chained launches. K must be a multiple of 8 and every row 16-byte aligned.
 #include "common.cuh"
 
 namespace {
@@ -18,6 +18,9 @@ __global__ void __launch_bounds__(BS_WARPS * 32)
 batched_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
                       TOut* __restrict__ out, int M, int N, int K, int lda, int ldw, int ldo, int batch,
                       long long a_batch, long long w_batch, long long o_batch) {
+    pdl_trigger();
+    pdl_wait();
+    A = after_wait(A);
     const long long column = (long long)blockIdx.x * BS_WARPS + (threadIdx.x >> 5);
     if (column >= (long long)batch * N) return;
     const int b = (int)(column / N), n = (int)(column - (long long)b * N);
@@ -67,12 +70,12 @@ extern "C" int mx_gemm_batched_skinny(const void* A, const void* W, void* out, i
     const long long columns = (long long)batch * N;
     const unsigned blocks = (unsigned)((columns + BS_WARPS - 1) / BS_WARPS);
     if (out_dtype == MX_DTYPE_F32)
-        batched_skinny_kernel<float><<<blocks, BS_WARPS * 32, 0, stream>>>(
-            (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, (float*)out, M, N, K, lda, ldw, ldo, batch, a_batch,
-            w_batch, o_batch);
+        mx_launch_chained(batched_skinny_kernel<float>, dim3(blocks), dim3(BS_WARPS * 32), 0, stream,
+                          (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, (float*)out, M, N, K, lda, ldw, ldo, batch,
+                          a_batch, w_batch, o_batch);
     else
-        batched_skinny_kernel<__nv_bfloat16><<<blocks, BS_WARPS * 32, 0, stream>>>(
-            (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, (__nv_bfloat16*)out, M, N, K, lda, ldw, ldo, batch,
-            a_batch, w_batch, o_batch);
+        mx_launch_chained(batched_skinny_kernel<__nv_bfloat16>, dim3(blocks), dim3(BS_WARPS * 32), 0, stream,
+                          (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, (__nv_bfloat16*)out, M, N, K, lda, ldw, ldo,
+                          batch, a_batch, w_batch, o_batch);
     return mx_launch_status();
 }

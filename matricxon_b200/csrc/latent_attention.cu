@@ -41,17 +41,19 @@ latent_prepare_kernel(const float* __restrict__ qd, int ld, const int* __restric
                       int rot_dims, int rank, int* status) {
     extern __shared__ float cs[];               // cos[half], sin[half]
     __shared__ float scratch[32];
+    pdl_trigger();
     const int t = blockIdx.x;
     const int half = rot_dims >> 1;
     const int dk = rank + rot;
-    const float pos = (float)positions[t];
+    const float pos = (float)positions[t];      // step metadata and constants: no kernel writes them
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         const float angle = pos * freq[i];
         cs[i] = cosf(angle) * amplitude;
         cs[half + i] = sinf(angle) * amplitude;
     }
     __syncthreads();
-    const float* row = qd + (size_t)t * ld;
+    pdl_wait();
+    const float* row = after_wait(qd) + (size_t)t * ld;
     const int qw = dim + rot;
     if (blockIdx.y > 0) {
         // blocks 1 .. of a token: LAT_PREP_HEADS query heads each
@@ -245,11 +247,11 @@ extern "C" int mx_latent_prepare(const float* qd, int ld, const int* positions, 
     const long long n_slots = n_pages * page_size;
     const dim3 grid(n_tokens, 1 + (n_heads + LAT_PREP_HEADS - 1) / LAT_PREP_HEADS);
     if (dtype == MX_DTYPE_F32)
-        latent_prepare_kernel<float><<<grid, LAT_THREADS, smem, stream>>>(
+        mx_launch_chained(latent_prepare_kernel<float>, grid, dim3(LAT_THREADS), smem, stream,
             qd, ld, positions, freq, amplitude, latent_weight, eps, cache ? slots : nullptr, (float*)cache, n_slots,
             (float*)q_plain, (float*)q_lat, n_heads, dim, rot, rot_dims, rank, status);
     else
-        latent_prepare_kernel<__nv_bfloat16><<<grid, LAT_THREADS, smem, stream>>>(
+        mx_launch_chained(latent_prepare_kernel<__nv_bfloat16>, grid, dim3(LAT_THREADS), smem, stream,
             qd, ld, positions, freq, amplitude, latent_weight, eps, cache ? slots : nullptr, (__nv_bfloat16*)cache,
             n_slots, (__nv_bfloat16*)q_plain, (__nv_bfloat16*)q_lat, n_heads, dim, rot, rot_dims, rank, status);
     return mx_launch_status();

@@ -47,6 +47,8 @@ struct LatentMmaParams {
     int* status;
     long long n_pages;
     int bt_stride, n_heads, rank, dk, page_size, window, n_splits;
+    int q_rows;                   // rows of queries kept in shared memory: 64, or 16 when no tile has more (decoding)
+    int stages;                   // key chunks in shared memory: 2, or 4 with q_rows = 16
     float scale;
 };
 
@@ -80,9 +82,9 @@ latent_attention_mma_kernel(const LatentMmaParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int dk = p.dk, rank = p.rank, heads = p.n_heads;
     const int ks = dk + 8;                                                    // padded row stride (elements)
-    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [64][ks]
-    __nv_bfloat16* k_s = q_s + LT_ROWS * ks;                                  // [2][32][ks]
-    __nv_bfloat16* p_s = k_s + 2 * LT_KEYS * ks;                              // [4][16][LT_PSTRIDE]
+    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [q_rows][ks]
+    __nv_bfloat16* k_s = q_s + p.q_rows * ks;                                 // [stages][32][ks]
+    __nv_bfloat16* p_s = k_s + p.stages * LT_KEYS * ks;                       // [4][16][LT_PSTRIDE]
     float* red_max = reinterpret_cast<float*>(p_s + 4 * 16 * LT_PSTRIDE);     // [4][2][16]
     float* red_sum = red_max + 4 * 2 * 16;                                    // [4][2][16]
 
@@ -93,6 +95,8 @@ latent_attention_mma_kernel(const LatentMmaParams p) {
     if (p.tiles) { seq = p.tiles[2 * blockIdx.x]; row0 = p.tiles[2 * blockIdx.x + 1]; }
     else { seq = blockIdx.x; row0 = blockIdx.y * LT_ROWS; }
     const int split = blockIdx.z;
+    pdl_trigger();
+    pdl_wait();                           // the queries and this step's keys come from the kernels before
     const int t0 = p.cu_q[seq];
     const int n_rows = (p.cu_q[seq + 1] - t0) * heads;
     if (row0 >= n_rows) return;                                               // a sequence without tokens in this step
@@ -108,7 +112,7 @@ latent_attention_mma_kernel(const LatentMmaParams p) {
 
     // ---- the tile's queries
     const int vecs = dk >> 3;
-    for (int item = tid; item < LT_ROWS * vecs; item += LT_THREADS) {
+    for (int item = tid; item < p.q_rows * vecs; item += LT_THREADS) {
         const int r = item / vecs, v = item - r * vecs;
         uint4 val = make_uint4(0, 0, 0, 0);
         if (r < rows_here) val = *reinterpret_cast<const uint4*>(p.q + (grow0 + r) * dk + v * 8);
@@ -158,13 +162,18 @@ latent_attention_mma_kernel(const LatentMmaParams p) {
     const bool rg_live = rg * 16 < rows_here;        // a row group beyond the tile's rows only helps with the copies
     const int col_base = half * (rank >> 1);
 
-    if (c_begin < c_end) issue(c_begin, 0);
-    cp_async_commit();
-    for (int chunk = c_begin; chunk < c_end; ++chunk) {
-        const int stage = (chunk - c_begin) & 1;
-        if (chunk + 1 < c_end) issue(chunk + 1, stage ^ 1);
+    // stages - 1 chunks are on their way while one is worked on (a group is committed every time, empty or
+    // not, so that the count of groups to wait for never changes)
+    const int ahead = p.stages - 1;
+    for (int i = 0; i < ahead; ++i) {
+        if (c_begin + i < c_end) issue(c_begin + i, i);
         cp_async_commit();
-        cp_async_wait<1>();
+    }
+    for (int chunk = c_begin; chunk < c_end; ++chunk) {
+        const int stage = (chunk - c_begin) % p.stages;
+        if (chunk + ahead < c_end) issue(chunk + ahead, (chunk - c_begin + ahead) % p.stages);
+        cp_async_commit();
+        if (ahead == 1) cp_async_wait<1>(); else cp_async_wait<3>();
         __syncthreads();                                                      // the chunk (and q_s) is in shared memory
         const __nv_bfloat16* kc = k_s + stage * LT_KEYS * ks;
         // ---- scores of this warp's 16 keys
@@ -309,17 +318,22 @@ latent_attention_mma_kernel(const LatentMmaParams p) {
 template <int NVT>
 int launch_latent_mma(const LatentMmaParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
     cudaFuncSetAttribute(latent_attention_mma_kernel<NVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    latent_attention_mma_kernel<NVT><<<grid, LT_THREADS, smem, stream>>>(p);
+    mx_launch_chained(latent_attention_mma_kernel<NVT>, grid, dim3(LT_THREADS), smem, stream, p);
     return mx_launch_status();
 }
 
 }  // namespace
 
+static size_t latent_mma_smem(int dk, int q_rows, int stages) {
+    return (size_t)(q_rows + stages * LT_KEYS) * (dk + 8) * 2 + 4 * 16 * LT_PSTRIDE * 2 + 2 * 4 * 2 * 16 * 4;
+}
+
 extern "C" int mx_latent_attention_mma_supported(int rank, int dk) {
-    const size_t smem = (size_t)(LT_ROWS + 2 * LT_KEYS) * (dk + 8) * 2 + 4 * 16 * LT_PSTRIDE * 2 + 2 * 4 * 2 * 16 * 4;
+    const size_t smem = latent_mma_smem(dk, LT_ROWS, 2);
     return rank > 0 && rank % 32 == 0 && rank <= 512 && dk >= rank && dk % 16 == 0 && smem <= 220 * 1024;
 }
 
+// few_rows != 0: every tile has at most 16 rows (see below).
 // tiles: [n_tiles][2] (sequence, first row) with grid_y = 1, or null with one block row per sequence and
 // grid_y row tiles per sequence (a fixed-size batch of decoding requests). scratch: float,
 // mx_attention_scratch_bytes(n_tokens, n_heads, rank, n_splits) bytes when n_splits > 1.
@@ -327,7 +341,7 @@ extern "C" int mx_latent_attention_mma(const void* q, const void* cache, long lo
                                        const int* block_tables, int bt_stride, const int* cu_q,
                                        const int* context_lens, const int* tiles, int n_tiles, int grid_y,
                                        int n_tokens, int n_heads, int rank, int dk, int window, float scale,
-                                       void* out, int n_splits, float* scratch, int* status,
+                                       void* out, int n_splits, float* scratch, int few_rows, int* status,
                                        cudaStream_t stream) {
     if (n_tokens <= 0 || n_tiles <= 0) return MX_OK;
     if (!mx_latent_attention_mma_supported(rank, dk))
@@ -340,7 +354,11 @@ extern "C" int mx_latent_attention_mma(const void* q, const void* cache, long lo
     p.block_tables = block_tables; p.cu_q = cu_q; p.context_lens = context_lens; p.tiles = tiles;
     p.status = status; p.n_pages = n_pages; p.bt_stride = bt_stride; p.n_heads = n_heads; p.rank = rank;
     p.dk = dk; p.page_size = page_size; p.window = window; p.n_splits = n_splits; p.scale = scale;
-    const size_t smem = (size_t)(LT_ROWS + 2 * LT_KEYS) * (dk + 8) * 2 + 4 * 16 * LT_PSTRIDE * 2 + 2 * 4 * 2 * 16 * 4;
+    // few_rows: the caller vouches that no tile has more than 16 rows (single tokens of at most 16 heads); the
+    // room of the other 48 query rows then goes to two more key chunks in flight
+    p.q_rows = few_rows ? 16 : LT_ROWS;
+    p.stages = (few_rows && latent_mma_smem(dk, 16, 4) <= 220 * 1024) ? 4 : 2;
+    const size_t smem = latent_mma_smem(dk, p.q_rows, p.stages);
     dim3 grid(n_tiles, tiles ? 1 : grid_y, n_splits);
     int rc;
     if (rank <= 128) rc = launch_latent_mma<8>(p, grid, smem, stream);

@@ -10,6 +10,7 @@
 // last product, `alpha` the weight of the skip path; the next sublayer reads `act` (a bfloat16 copy
 // when serving; on the 32-bit path it reads x itself and act is null).
 //
+// The float4 form of the post-norm sum takes part in chained launches (programmatic dependent launch).
 // One block per row; sums of squares are float and their order depends on the thread layout alone,
 // so a row's result does not depend on the other rows of the step.
 // mx_cast_rows rounds a float matrix to the activation dtype (the first sublayer's input).
@@ -70,6 +71,10 @@ __global__ void rmsnorm_sum_vec_kernel(float* x, const float* __restrict__ acc, 
                                        const float* __restrict__ weight, float offset, TAct* act, int hidden,
                                        float eps) {
     __shared__ float scratch[32];
+    pdl_trigger();
+    pdl_wait();
+    x = after_wait(x);
+    acc = after_wait(acc);
     const int r = blockIdx.x;
     float4* xr = reinterpret_cast<float4*>(x + (size_t)r * hidden);
     const float4* ar = reinterpret_cast<const float4*>(acc + (size_t)r * hidden);
@@ -140,11 +145,11 @@ extern "C" int mx_rmsnorm_sum(float* x, const float* acc, float alpha, const flo
         if (n_rows <= 64) vthreads = (hidden / 4 + 31) / 32 * 32;
         vthreads = vthreads > 1024 ? 1024 : vthreads;
         if (act == nullptr || act_dtype == MX_DTYPE_F32)
-            rmsnorm_sum_vec_kernel<float><<<n_rows, vthreads, 0, stream>>>(x, acc, alpha, weight, offset, (float*)act,
-                                                                         hidden, eps);
+            mx_launch_chained(rmsnorm_sum_vec_kernel<float>, dim3(n_rows), dim3(vthreads), 0, stream, x, acc, alpha,
+                              weight, offset, (float*)act, hidden, eps);
         else
-            rmsnorm_sum_vec_kernel<__nv_bfloat16><<<n_rows, vthreads, 0, stream>>>(
-                x, acc, alpha, weight, offset, (__nv_bfloat16*)act, hidden, eps);
+            mx_launch_chained(rmsnorm_sum_vec_kernel<__nv_bfloat16>, dim3(n_rows), dim3(vthreads), 0, stream, x, acc,
+                              alpha, weight, offset, (__nv_bfloat16*)act, hidden, eps);
         return mx_launch_status();
     }
     const int threads = threads_for(hidden);

@@ -671,8 +671,10 @@ def latent_tile_list(q_lens: list[int], n_heads: int) -> list[int]:
 def latent_attention_mma(q_lat: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor,
                          cu_q: torch.Tensor, context_lens: torch.Tensor, tiles: torch.Tensor | None,
                          n_tiles: int, rank: int, window: int | None, scale: float, out: torch.Tensor,
-                         status: torch.Tensor, n_splits: int = 1, scratch: torch.Tensor | None = None) -> None:
-    """``latent_attention`` on the tensor cores (bfloat16). ``tiles`` is int32 [n_tiles, 2] from
+                         status: torch.Tensor, n_splits: int = 1, scratch: torch.Tensor | None = None,
+                         few_rows: bool = False) -> None:
+    """``latent_attention`` on the tensor cores (bfloat16). ``few_rows``: the caller vouches that every
+    sequence brings at most 16 (token, head) rows, which lets the kernel keep more keys in flight. ``tiles`` is int32 [n_tiles, 2] from
     ``latent_tile_list``; None means that tile i is sequence i (a fixed-size batch of decoding requests,
     ``n_tiles`` sequences). ``n_splits`` > 1 shares every tile's keys out between that many blocks;
     ``scratch`` (float32, ``attention_scratch_bytes(tokens, heads, rank, n_splits)``) takes their parts."""
@@ -699,7 +701,7 @@ def latent_attention_mma(q_lat: torch.Tensor, cache: torch.Tensor, block_tables:
         _ptr(q_lat), _ptr(cache), cache.shape[0], cache.shape[3], _ptr(block_tables), block_tables.stride(0),
         _ptr(cu_q), _ptr(context_lens), _ptr(tiles), n_tiles, (n_heads + 63) // 64, n, n_heads, rank, dk,
         int(window or 0), float(scale), _ptr(out), int(n_splits), _ptr(scratch) if n_splits > 1 else None,
-        _ptr(status), _stream()), "latent_attention_mma")
+        1 if few_rows else 0, _ptr(status), _stream()), "latent_attention_mma")
     _launched(2 if n_splits > 1 else 1)
 
 

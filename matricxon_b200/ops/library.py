@@ -50,7 +50,7 @@ _SIGNATURES: dict[str, tuple[list, object]] = {
     "mx_cast_rows": ([P, P, L, P], I),
     "mx_latent_prepare": ([P, I, P, P, F, P, F, P, P, L, I, P, P, I, I, I, I, I, I, I, P, P], I),
     "mx_latent_attention_mma_supported": ([I, I], I),
-    "mx_latent_attention_mma": ([P, P, L, I, P, I, P, P, P, I, I, I, I, I, I, I, F, P, I, P, P, P], I),
+    "mx_latent_attention_mma": ([P, P, L, I, P, I, P, P, P, I, I, I, I, I, I, I, F, P, I, P, I, P, P], I),
     "mx_latent_attention": ([P, P, I, L, I, P, I, P, P, I, I, I, I, I, F, P, P, P], I),
     "mx_qk_norm_kv_write": ([P, I, P, P, F, P, P, L, I, P, I, I, I, I, I, I, I, P, P], I),
     "mx_sigmoid_gate": ([P, P, I, P, I, I, I, I, I, P], I),

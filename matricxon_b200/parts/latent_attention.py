@@ -12,12 +12,18 @@ value-side per-head product, and the output projection. Scores, softmax, norm an
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from matricxon_b200.ops import kernels
 from matricxon_b200.ops.linear import EPILOGUE_F32, EPILOGUE_RESIDUAL, batched_linear, linear
 from matricxon_b200.parts.base import KVCacheRequest, Mixer, build_part, register_part
 from matricxon_b200.weights.loader import WeightSpec
+
+
+# fewest chunks of 32 keys a key split is given (MATRICXON_LATENT_SPLIT_CHUNKS, for measurements)
+_SPLIT_CHUNKS = max(1, int(os.environ.get("MATRICXON_LATENT_SPLIT_CHUNKS", "8")))
 
 
 @register_part("mixer", "latent_attention")
@@ -71,10 +77,10 @@ class LatentAttention(Mixer):
 
     def _splits(self, ctx, n_tiles: int):
         """Key splits: a block fills an SM's shared memory, so few tiles (decoding) leave SMs idle unless
-        each tile's keys are shared out; a split keeps at least eight chunks of 32 keys."""
+        each tile's keys are shared out; a split keeps at least ``_SPLIT_CHUNKS`` chunks of 32 keys."""
         span = ctx.max_kv_len if self.spec.window is None else min(ctx.max_kv_len, self.spec.window)
         blocks = n_tiles * (-(-self.spec.num_heads // 64) if ctx.padded else 1)
-        n_splits = max(1, min(ctx.sm_count // max(blocks, 1), (span // 32 + 1) // 8, 64))
+        n_splits = max(1, min(ctx.sm_count // max(blocks, 1), (span // 32 + 1) // _SPLIT_CHUNKS, 64))
         if n_splits == 1:
             return 1, None
         return n_splits, ctx.scratch(kernels.attention_scratch_bytes(ctx.n_tokens, self.spec.num_heads,
@@ -99,8 +105,10 @@ class LatentAttention(Mixer):
         if kernels.latent_attention_mma_supported(rt.dtype, rank, self.key_width):
             tiles, n_tiles = self._tiles(ctx)
             n_splits, scratch = self._splits(ctx, n_tiles)
+            few_rows = heads <= 16 and (ctx.padded or max(ctx.host.q_lens) * heads <= 16)
             kernels.latent_attention_mma(q_lat, binding.kv, tables, ctx.cu_q, ctx.context_lens, tiles, n_tiles, rank,
-                                         s.window, s.scale, mixed, ctx.status, n_splits=n_splits, scratch=scratch)
+                                         s.window, s.scale, mixed, ctx.status, n_splits=n_splits, scratch=scratch,
+                                         few_rows=few_rows)
         else:       # the 32-bit path, and sizes the tensor-core kernel does not take
             kernels.latent_attention(q_lat, binding.kv, tables, ctx.tok_seq, ctx.positions, rank, s.window,
                                      s.scale, mixed, ctx.status)

@@ -112,7 +112,7 @@ def test_rms_norm_and_post_norm_sum(dtype, hidden, offset):
 
 
 def _latent_case(dtype, n_heads, rank, rot, page_size, window, contexts, q_lens, seed, spike=None,
-                 tensor_cores=False, n_splits=1, no_list=False):
+                 tensor_cores=False, n_splits=1, no_list=False, few_rows=False):
     """Queries and a paged latent cache with shuffled pages; returns what the kernel gave and the plain sums.
     ``spike`` = (sequence, query offset, key position): that key's vector is made to dominate the query's
     scores if the query sees it."""
@@ -159,7 +159,7 @@ def _latent_case(dtype, n_heads, rank, rot, page_size, window, contexts, q_lens,
         kernels.latent_attention_mma(q_all.to(dtype).to(DEVICE), cache.to(dtype).to(DEVICE), tables.to(DEVICE), cu_q,
                                      torch.tensor(contexts, dtype=torch.int32, device=DEVICE), tiles,
                                      len(q_lens) if no_list else len(flat) // 2, rank, window, scale, out, status,
-                                     n_splits=n_splits, scratch=scratch)
+                                     n_splits=n_splits, scratch=scratch, few_rows=few_rows)
     else:
         kernels.latent_attention(q_all.to(dtype).to(DEVICE), cache.to(dtype).to(DEVICE), tables.to(DEVICE),
                                  torch.tensor(tok_seq, dtype=torch.int32, device=DEVICE),
@@ -199,6 +199,11 @@ def test_latent_attention_on_tensor_cores(n_heads, rank, rot, page_size, window,
                                 q_lens=[1, 1, 1, 1], seed=rank + 1, tensor_cores=True, n_splits=n_splits,
                                 no_list=True)
     assert torch.allclose(got, want, rtol=0.03, atol=0.03)
+    if n_heads <= 16:       # single tokens of few heads: the deeper pipeline of key chunks, over many chunks
+        got, want, _ = _latent_case(torch.bfloat16, n_heads, rank, rot, page_size, window and 8 * window,
+                                    contexts=[300, 70, 0, 519], q_lens=[1, 1, 1, 1], seed=rank + 2, tensor_cores=True,
+                                    n_splits=n_splits, no_list=n_splits == 1, few_rows=True)
+        assert torch.allclose(got, want, rtol=0.03, atol=0.03)
 
 
 @pytest.mark.parametrize("decode", [False, True])
