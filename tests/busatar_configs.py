@@ -62,7 +62,24 @@ MODEL_Y = model(128, 257, 3.0, 1e-5, [
     latent(9, 16, 16, 136, 16, window=16, scale=0.3, ff=64),
 ])
 
-MODELS = {"X": MODEL_X, "Y": MODEL_Y}
+# sizes that are multiples of nothing useful: width 100, odd vocabulary, heads of 12 and 20, a rotated part of
+# 6, a latent of 20, three blocks of 20 channels, two taps
+MODEL_Z = model(100, 131, 2.0, 1e-5, [
+    latent(5, 12, 6, 20, 10, window=40, scale=0.3, scaling={"factor": 2.0, "original": 24, "fast": 3.0, "slow": 1.5}, ff=52),
+    recurrent(60, 3, 2),
+    gated(6, 3, 20, 12, window=50, scale=0.25, ff=76, limit=1.2),
+])
+
+# a middle size for long prompts: products of more than a thousand rows, tensor-core latent attention
+# (latent 64, key 96), 128-wide attention heads in a group of two, a recurrence in many chunks
+MODEL_W = model(256, 640, 2.0, 1e-5, [
+    latent(4, 48, 32, 64, 48, window=200, scale=0.11, scaling={"factor": 8.0, "original": 512, "fast": 32.0, "slow": 1.0}, ff=512),
+    gated(4, 2, 128, 128, window=150, scale=0.09, ff=384),
+    recurrent(192, 3, 4, ff=256),
+    latent(2, 64, 16, 128, 32, window=1500, scale=0.1),
+])
+
+MODELS = {"X": MODEL_X, "Y": MODEL_Y, "Z": MODEL_Z, "W": MODEL_W}
 INIT = RandomInit(weight_std=0.08, bias_std=0.3, norm_weight_std=0.1, norm_bias_std=0.1)
 
 

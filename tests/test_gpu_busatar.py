@@ -374,6 +374,24 @@ def test_long_decoding(run):
     run.check("lb", b)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name, length", [("Z", 330), ("W", 1100)])
+def test_long_prompts_and_awkward_sizes(name, length, dtype):
+    """A prompt long enough for the prompt-sized product kernels, the chunked recurrence and many attention
+    tiles: whole, then in uneven portions with the tail decoded token by token."""
+    raw = MODELS[name]
+    run = Run(raw, draw(raw, seed=21, sharpen=2.0), dtype, max_tokens=2 * (length + 64))
+    tokens = ids(length, raw["vocab"], seed=5)
+    run.step([("whole", tokens)], end=["whole"])
+    run.check("whole", tokens)
+    cuts = [0, length // 3 + 1, length // 3 + 3, length - 40]
+    for a, b in zip(cuts, cuts[1:]):
+        run.step([("cut", tokens[a:b])])
+    for i in range(length - 40, length):
+        run.step([("cut", tokens[i:i + 1])], end=["cut"] if i == length - 1 else [])
+    run.check("cut", tokens)
+
+
 def test_greedy_generation_through_the_engine_entry_point():
     from matricxon_b200 import ChatEngine, GenerationRequest, SamplingConfig
 
