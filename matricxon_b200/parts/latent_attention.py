@@ -23,7 +23,7 @@ from matricxon_b200.weights.loader import WeightSpec
 
 
 # fewest chunks of 32 keys a key split is given (MATRICXON_LATENT_SPLIT_CHUNKS, for measurements)
-_SPLIT_CHUNKS = max(1, int(os.environ.get("MATRICXON_LATENT_SPLIT_CHUNKS", "8")))
+_SPLIT_CHUNKS = max(1, int(os.environ.get("MATRICXON_LATENT_SPLIT_CHUNKS", "4")))
 
 
 @register_part("mixer", "latent_attention")

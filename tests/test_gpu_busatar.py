@@ -204,6 +204,11 @@ def test_latent_attention_on_tensor_cores(n_heads, rank, rot, page_size, window,
                                     contexts=[300, 70, 0, 519], q_lens=[1, 1, 1, 1], seed=rank + 2, tensor_cores=True,
                                     n_splits=n_splits, no_list=n_splits == 1, few_rows=True)
         assert torch.allclose(got, want, rtol=0.03, atol=0.03)
+    if n_heads <= 3:        # ... and a few tokens of few heads, still no more than 16 rows a sequence
+        got, want, _ = _latent_case(torch.bfloat16, n_heads, rank, rot, page_size, window, contexts=[30, 0, 64, 7],
+                                    q_lens=[5, 1, 2, 4], seed=rank + 3, tensor_cores=True, n_splits=n_splits,
+                                    few_rows=True)
+        assert torch.allclose(got, want, rtol=0.03, atol=0.03)
 
 
 @pytest.mark.parametrize("decode", [False, True])
