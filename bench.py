@@ -11,6 +11,10 @@ on the host each step). ``prefill`` is one 2,048-token prompt in one step; ``roo
 relates the decode step's necessary bytes (every weight once plus the live cache) to its
 time; ``points`` adds decoding at batch 1 and 64. Between timed iterations the working set
 (6 GB of weights) is larger than L2, so nothing is flushed explicitly.
+
+``--compare busatar`` runs another workload instead and prints its own JSON line: the Busatar architecture
+beside StarCoder2 at equal width, heads, layers and feed-forward parameters (prefill of 2,048 tokens in one
+step and in 512-token steps, decode steps at several batch sizes; random weights of both).
 """
 
 from __future__ import annotations

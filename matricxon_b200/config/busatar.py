@@ -102,8 +102,9 @@ class BusatarLayer:
             mask = mixer.get("mask")
             if not isinstance(mask, dict):
                 raise ConfigError(f"{where}.mixer: 'mask' must be an object with 'size'")
-            fields.update(heads=m.integer("heads", minimum=1), dim=m.integer("dim", minimum=1),
-                          vdim=m.integer("vdim", minimum=1), scale=m.number("scale", positive=True),
+            dim = m.integer("dim", minimum=1)
+            fields.update(heads=m.integer("heads", minimum=1), dim=dim,
+                          vdim=m.integer("vdim", dim, minimum=1), scale=m.number("scale", positive=True),
                           window=ConfigReader(mask, where + ".mixer.mask").integer("size", minimum=1))
         if kind == "latent_attention":
             rot_dim = m.integer("rot_dim", minimum=0)
@@ -112,7 +113,7 @@ class BusatarLayer:
                 raise ConfigError(f"{where}.mixer: rot.dims ({rot.dims}) exceeds rot_dim ({rot_dim})")
             fields.update(rot_dim=rot_dim, kv_rank=m.integer("kv_rank", minimum=1), rot=rot)
         elif kind == "attention":
-            fields.update(kv_heads=m.integer("kv_heads", minimum=1))
+            fields.update(kv_heads=m.integer("kv_heads", fields["heads"], minimum=1))
             if fields["heads"] % fields["kv_heads"]:
                 raise ConfigError(f"{where}.mixer: heads ({fields['heads']}) must be a multiple of kv_heads "
                                   f"({fields['kv_heads']})")

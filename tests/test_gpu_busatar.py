@@ -14,7 +14,7 @@ import torch
 import plain_busatar as plain
 from busatar_configs import MODELS, draw, gated, ids, latent, recurrent, single_layer
 from matricxon_b200.config.registry import config_from_dict
-from matricxon_b200.engine.core import EngineCore, model_from_tensors
+from matricxon_b200.engine.core import model_from_tensors
 from matricxon_b200.engine.replay import TraceReplayer
 from matricxon_b200.ops import kernels
 from trace_utils import ROOT
