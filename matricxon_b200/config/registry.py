@@ -101,6 +101,14 @@ def _register_builtin() -> None:
         config_class=BusatarConfig,
         build_model=_build_decoder,
     ))
+    from matricxon_b200.config.parunex import ParunexConfig
+
+    register_architecture(ArchitectureEntry(
+        name="Parunex",
+        aliases=("parunex",),
+        config_class=ParunexConfig,
+        build_model=_build_decoder,
+    ))
 
 
 _register_builtin()

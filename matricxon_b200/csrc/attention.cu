@@ -40,6 +40,8 @@ struct AttnParams {
     int q_stride, out_stride, bt_stride;
     int n_heads, n_kv_heads, head_dim, page_size, window, n_splits;
     float scale;
+    float softcap;            // > 0: scores become softcap * tanh(score / softcap) before the softmax
+    const float* sink;        // [n_heads] or null: exp(sink[h]) joins the softmax's denominator, with no value
 };
 
 template <typename T> struct Vec16;  // 16 bytes of T
@@ -208,7 +210,9 @@ paged_attention_kernel(const AttnParams p) {
             for (int hs = 0; hs < HEADS_PER_WARP; ++hs) {
                 const int h = warp + hs * ATT_WARPS;
                 if (h < gc) {
-                    const float sv = valid ? s[hs] * p.scale : -INFINITY;
+                    float sv = s[hs] * p.scale;
+                    if (p.softcap > 0.f) sv = p.softcap * tanhf(sv / p.softcap);
+                    sv = valid ? sv : -INFINITY;
                     const float m_new = fmaxf(m_run[hs], warp_max(sv));
                     const float pj = valid ? expf(sv - m_new) : 0.f;
                     const float alpha = (m_run[hs] == -INFINITY) ? 0.f : expf(m_run[hs] - m_new);
@@ -269,7 +273,11 @@ paged_attention_kernel(const AttnParams p) {
             if (d < hd) {
 #pragma unroll
                 for (int h = 0; h < GH; ++h)
-                    if (h < gc) orow[(size_t)h * hd + d] = from_float<T>(acc[h][slot] / l_s[h]);
+                    if (h < gc) {
+                        // the sink counts once in the denominator and brings no value
+                        const float extra = p.sink ? expf(p.sink[head0 + h] - m_s[h]) : 0.f;
+                        orow[(size_t)h * hd + d] = from_float<T>(acc[h][slot] / (l_s[h] + extra));
+                    }
             }
         }
     } else {
@@ -291,7 +299,8 @@ paged_attention_kernel(const AttnParams p) {
 template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part_o,
                                        const float* __restrict__ part_ml, T* __restrict__ out,
-                                       int out_stride, int n_heads, int head_dim, int n_splits) {
+                                       int out_stride, int n_heads, int head_dim, int n_splits,
+                                       const float* __restrict__ sink) {
     // One trip to memory: the maxima and sums of the splits (one per thread, into shared memory) and this
     // thread's value of the first MERGE_AHEAD splits set out together; only then is anything combined.
     // Each split's weight exp(max_s - max) is computed once, by the thread that fetched its maximum.
@@ -329,6 +338,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o,
             total += (s < MERGE_KEPT ? split_sum[s] : part_ml[(base + s) * 2 + 1]) * w;
         }
         total = warp_sum(total);
+        if (sink) total += expf(sink[h] - m);           // counted once, whatever the number of splits
         if (lane == 0) { total_max = m; total_sum = total; }
     }
     __syncthreads();
@@ -369,7 +379,8 @@ constexpr int MERGE_ROW_SPLITS = 8, MERGE_ROW_WARPS = 8;
 template <typename T>
 __global__ void __launch_bounds__(MERGE_ROW_WARPS * 32)
 attention_merge_rows_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, T* __restrict__ out,
-                            int out_stride, int n_heads, int head_dim, int n_splits, int n_pairs) {
+                            int out_stride, int n_heads, int head_dim, int n_splits, int n_pairs,
+                            const float* __restrict__ sink) {
     pdl_trigger();
     pdl_wait();
     part_o = after_wait(part_o);
@@ -394,6 +405,7 @@ attention_merge_rows_kernel(const float* __restrict__ part_o, const float* __res
         weight[s] = weight[s] == -INFINITY ? 0.f : expf(weight[s] - m);
         total += sums[s] * weight[s];
     }
+    if (sink) total += expf(sink[h] - m);
     const float inv = 1.f / total;
     for (int d = 4 * lane; d < head_dim; d += 128) {
         float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -416,17 +428,17 @@ attention_merge_rows_kernel(const float* __restrict__ part_o, const float* __res
 // Which of the two merges a step takes: the many-row one from 1,024 (token, head) pairs on, where it fits.
 template <typename T>
 int launch_merge(const float* part_o, const float* part_ml, T* out, int out_stride, int n_tokens, int n_heads,
-                 int head_dim, int n_splits, cudaStream_t stream) {
+                 int head_dim, int n_splits, const float* sink, cudaStream_t stream) {
     const long long pairs = (long long)n_tokens * n_heads;
     if (pairs >= 1024 && pairs < (1LL << 31) && n_splits <= MERGE_ROW_SPLITS && head_dim % 4 == 0 &&
         reinterpret_cast<uintptr_t>(part_o) % 16 == 0) {
         const int blocks = (int)((pairs + MERGE_ROW_WARPS - 1) / MERGE_ROW_WARPS);
         mx_launch_chained(attention_merge_rows_kernel<T>, dim3(blocks), dim3(MERGE_ROW_WARPS * 32), 0, stream, part_o,
-                          part_ml, out, out_stride, n_heads, head_dim, n_splits, (int)pairs);
+                          part_ml, out, out_stride, n_heads, head_dim, n_splits, (int)pairs, sink);
         return mx_launch_status();
     }
     mx_launch_chained(attention_merge_kernel<T>, dim3(n_tokens, n_heads), dim3(128), 0, stream, part_o, part_ml, out,
-                      out_stride, n_heads, head_dim, n_splits);
+                      out_stride, n_heads, head_dim, n_splits, sink);
     return mx_launch_status();
 }
 
@@ -451,7 +463,7 @@ int launch_attention(const AttnParams& p, int n_tokens, cudaStream_t stream) {
     int rc = mx_launch_status();
     if (rc != MX_OK || p.n_splits == 1) return rc;
     return launch_merge<T>(p.part_o, p.part_ml, (T*)p.out, p.out_stride, n_tokens, p.n_heads, p.head_dim, p.n_splits,
-                           stream);
+                           p.sink, stream);
 }
 
 }  // namespace
@@ -467,7 +479,8 @@ extern "C" int mx_paged_attention(const void* q, int dtype, int q_stride, const 
                                   int bt_stride, const int* tok_seq, const int* positions,
                                   int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                                   int window, float scale, void* out, int out_stride,
-                                  int n_splits, float* scratch, int* status, cudaStream_t stream) {
+                                  int n_splits, float* scratch, int* status, float softcap, const float* sink,
+                                  cudaStream_t stream) {
     if (n_tokens <= 0) return MX_OK;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
         MX_REFUSE("attention: %d heads are not a multiple of %d kv heads", n_heads, n_kv_heads);
@@ -486,6 +499,7 @@ extern "C" int mx_paged_attention(const void* q, int dtype, int q_stride, const 
     p.n_pages = n_pages; p.q_stride = q_stride; p.out_stride = out_stride; p.bt_stride = bt_stride;
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim; p.page_size = page_size;
     p.window = window; p.n_splits = n_splits; p.scale = scale;
+    p.softcap = softcap; p.sink = sink;
     const bool two = head_dim > ATT_THREADS;
     if (dtype == MX_DTYPE_F32)
         return two ? launch_attention<float, 2>(p, n_tokens, stream) : launch_attention<float, 1>(p, n_tokens, stream);
@@ -494,12 +508,19 @@ extern "C" int mx_paged_attention(const void* q, int dtype, int q_stride, const 
 }
 
 // The merge step alone, for kernels in other files that write partials in this layout.
+extern "C" int mx_attention_merge_bf16_sink(const float* part_o, const float* part_ml, void* out,
+                                            int out_stride, int n_tokens, int n_heads, int head_dim,
+                                            int n_splits, const float* sink, cudaStream_t stream) {
+    if (n_tokens <= 0) return MX_OK;
+    return launch_merge<__nv_bfloat16>(part_o, part_ml, (__nv_bfloat16*)out, out_stride, n_tokens, n_heads, head_dim,
+                                       n_splits, sink, stream);
+}
+
 extern "C" int mx_attention_merge_bf16(const float* part_o, const float* part_ml, void* out,
                                        int out_stride, int n_tokens, int n_heads, int head_dim,
                                        int n_splits, cudaStream_t stream) {
-    if (n_tokens <= 0) return MX_OK;
-    return launch_merge<__nv_bfloat16>(part_o, part_ml, (__nv_bfloat16*)out, out_stride, n_tokens, n_heads, head_dim,
-                                       n_splits, stream);
+    return mx_attention_merge_bf16_sink(part_o, part_ml, out, out_stride, n_tokens, n_heads, head_dim, n_splits,
+                                        nullptr, stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -569,5 +590,5 @@ extern "C" int mx_paged_attention_static(const void* q, int dtype, int q_stride,
     if (rc != MX_OK) return rc;
     return mx_paged_attention(q, dtype, q_stride, cache, n_pages, page_size, block_tables, bt_stride,
                               tok_seq, positions, n_tokens, n_heads, n_kv_heads, head_dim, window,
-                              scale, out, out_stride, n_splits, scratch, status, stream);
+                              scale, out, out_stride, n_splits, scratch, status, 0.f, nullptr, stream);
 }

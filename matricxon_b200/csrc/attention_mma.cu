@@ -65,6 +65,10 @@ struct MmaAttnParams {
     int n_tiles, q_stride, out_stride, bt_stride;
     int n_heads, n_kv_heads, page_size, page_shift, window, n_splits;
     float scale_log2;            // scale * log2(e)
+    // capped scores: cap_log2 = cap * log2(e) > 0 turns score * scale into cap * tanh(score * scale / cap)
+    // (cap_in = scale / cap), already in the units of the exponential; 0: no cap
+    float cap_log2, cap_in;
+    const float* sink;           // [heads] or null: exp(sink[h]) joins the softmax's denominator, with no value
 };
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2,
@@ -324,6 +328,15 @@ attention_mma_kernel(const MmaAttnParams p) {
                 for (int b = 0; b < 4; ++b)
                     mma_bf16(s[ch][b], qf[0][kb].z, qf[1][kb].z, qf[0][kb].w, qf[1][kb].w, kf[b].z, kf[b].w);
             }
+        const float scale_log2 = p.cap_log2 > 0.f ? 1.f : p.scale_log2;
+        if (p.cap_log2 > 0.f) {
+#pragma unroll
+            for (int ch = 0; ch < NCH; ++ch)
+#pragma unroll
+                for (int b = 0; b < 4; ++b)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s[ch][b][e] = p.cap_log2 * tanh_by_exp2(s[ch][b][e] * p.cap_in);
+        }
         // mask (only where the chunks cross an edge), running max and sum for rows g, g + 8
         float m_new[2] = {m_run[0], m_run[1]};
         const bool plain = rows_full && c0 >= all_lo && c0 + NCH * CHUNK - 1 <= all_hi;
@@ -351,8 +364,8 @@ attention_mma_kernel(const MmaAttnParams p) {
                         raw_max[i] = fmaxf(raw_max[i], s[ch][b][e]);
                     }
         }
-        m_new[0] = fmaxf(m_new[0], raw_max[0] * p.scale_log2);
-        m_new[1] = fmaxf(m_new[1], raw_max[1] * p.scale_log2);
+        m_new[0] = fmaxf(m_new[0], raw_max[0] * scale_log2);
+        m_new[1] = fmaxf(m_new[1], raw_max[1] * scale_log2);
         float alpha[2], sum[2] = {0.f, 0.f}, m_use[2];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
@@ -368,7 +381,7 @@ attention_mma_kernel(const MmaAttnParams p) {
             for (int b = 0; b < 4; ++b)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float pv = fast_exp2(fmaf(s[ch][b][e], p.scale_log2, -m_use[e >> 1]));
+                    const float pv = fast_exp2(fmaf(s[ch][b][e], scale_log2, -m_use[e >> 1]));
                     s[ch][b][e] = pv;
                     sum[e >> 1] += pv;
                 }
@@ -518,7 +531,8 @@ attention_mma_kernel(const MmaAttnParams p) {
             const int row = tile_row0 + r;
             const int tok = row / group, head = kh * group + (row - tok * group);
             if (p.n_splits == 1) {
-                const float inv = 1.f / sum_of[r];
+                // the sink counts once in the denominator (maxima are in units of log2)
+                const float inv = 1.f / (sum_of[r] + (p.sink ? fast_exp2(p.sink[head] * 1.4426950408889634f - max_of[r]) : 0.f));
                 uint2 packed;
                 packed.x = pack_bf16(acc.x * inv, acc.y * inv);
                 packed.y = pack_bf16(acc.z * inv, acc.w * inv);
@@ -574,7 +588,7 @@ attention_mma_kernel(const MmaAttnParams p) {
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             if (!r_valid[i]) continue;
-            const float inv = 1.f / l_run[i];
+            const float inv = 1.f / (l_run[i] + (p.sink ? fast_exp2(p.sink[kh * group + r_head[i]] * 1.4426950408889634f - m_run[i]) : 0.f));
             __nv_bfloat16* orow = p.out + (size_t)(q_start + r_tok[i]) * p.out_stride +
                                   (size_t)(kh * group + r_head[i]) * HD;
 #pragma unroll
@@ -623,9 +637,9 @@ int launch_mma(const MmaAttnParams& p, cudaStream_t stream) {
 
 }  // namespace
 
-extern "C" int mx_attention_merge_bf16(const float* part_o, const float* part_ml, void* out,
-                                       int out_stride, int n_tokens, int n_heads, int head_dim,
-                                       int n_splits, cudaStream_t stream);
+extern "C" int mx_attention_merge_bf16_sink(const float* part_o, const float* part_ml, void* out,
+                                            int out_stride, int n_tokens, int n_heads, int head_dim,
+                                            int n_splits, const float* sink, cudaStream_t stream);
 
 // `narrow` != 0: every tile has at most 16 rows (decode tokens); the eight warps of a block
 // share them and take the key chunks in turn. Otherwise tiles are 64 rows, 16 per warp.
@@ -635,7 +649,8 @@ extern "C" int mx_paged_attention_mma(const void* q, int q_stride, const void* c
                                       const int* tiles, int n_tiles, int narrow, int n_tokens,
                                       int n_heads, int n_kv_heads, int head_dim, int window,
                                       float scale, void* out, int out_stride, int n_splits,
-                                      float* scratch, int* status, cudaStream_t stream) {
+                                      float* scratch, int* status, float softcap, const float* sink,
+                                      cudaStream_t stream) {
     if (n_tiles <= 0 || n_tokens <= 0) return MX_OK;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
         MX_REFUSE("attention: %d heads are not a multiple of %d kv heads", n_heads, n_kv_heads);
@@ -658,10 +673,13 @@ extern "C" int mx_paged_attention_mma(const void* q, int q_stride, const void* c
     p.page_size = page_size; p.page_shift = page_size == 8 ? 3 : (page_size == 16 ? 4 : 5);
     p.window = window; p.n_splits = n_splits;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
+    p.cap_in = softcap > 0.f ? scale / softcap : 0.f;
+    p.sink = sink;
     int rc;
     if (head_dim == 64) rc = narrow ? launch_mma<64, true>(p, stream) : launch_mma<64, false>(p, stream);
     else rc = narrow ? launch_mma<128, true>(p, stream) : launch_mma<128, false>(p, stream);
     if (rc != MX_OK || n_splits == 1) return rc;
-    return mx_attention_merge_bf16(p.part_o, p.part_ml, out, out_stride, n_tokens, n_heads, head_dim,
-                                   n_splits, stream);
+    return mx_attention_merge_bf16_sink(p.part_o, p.part_ml, out, out_stride, n_tokens, n_heads, head_dim,
+                                        n_splits, sink, stream);
 }

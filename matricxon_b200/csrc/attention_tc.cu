@@ -81,6 +81,10 @@ struct AtParams {
     long long n_pages;
     int out_stride, bt_stride, n_heads, n_kv_heads, group, tokens_per_tile, page_size, page_shift, window;
     float scale_log2;
+    // capped scores: cap_log2 = cap * log2(e) > 0 turns score * scale into cap * tanh(score * scale / cap)
+    // (cap_in = scale / cap), already in the units of the exponential; 0: no cap
+    float cap_log2, cap_in;
+    const float* sink;           // [heads] or null: exp(sink[h]) joins the softmax's denominator, with no value
 };
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -471,6 +475,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
                 tmem_load32(s_addr + 64 * part, sc);
                 tmem_load32(s_addr + 64 * part + 32, sc + 32);
                 asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                if (p.cap_log2 > 0.f) {
+#pragma unroll
+                    for (int c = 0; c < 64; ++c) sc[c] = p.cap_log2 * tanh_by_exp2(sc[c] * p.cap_in);
+                }
                 if (edge) {
 #pragma unroll
                     for (int c = 0; c < 64; ++c) {
@@ -494,7 +502,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
                 alive = false;
                 break;                                  // all 256 threads see the flag after the barrier
             }
-            mx = fmaxf(mx, half_max[j & 1][part ^ 1][row]) * p.scale_log2;
+            const float scale_log2 = p.cap_log2 > 0.f ? 1.f : p.scale_log2;
+            mx = fmaxf(mx, half_max[j & 1][part ^ 1][row]) * scale_log2;
             const bool jump = mx > m_ref + AT_JUMP || (m_ref == -INFINITY && mx > -INFINITY);
             const float m_new = jump ? mx : m_ref;
             // O may only be touched while no P V is running: the rare rescaling waits for the previous one
@@ -526,8 +535,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
                 unsigned packed[32];
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
-                    const float e0 = at_exp2(fmaf(sc[2 * c], p.scale_log2, -m_use));
-                    const float e1 = at_exp2(fmaf(sc[2 * c + 1], p.scale_log2, -m_use));
+                    const float e0 = at_exp2(fmaf(sc[2 * c], scale_log2, -m_use));
+                    const float e1 = at_exp2(fmaf(sc[2 * c + 1], scale_log2, -m_use));
                     sum0 += e0;
                     sum1 += e1;
                     packed[c] = at_pack(e0, e1);
@@ -588,7 +597,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
             }
         } else if (alive) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            // the sink counts once in the denominator (the reference maximum is in units of log2)
+            const float extra = (p.sink && valid && l_run > 0.f)
+                                    ? at_exp2(p.sink[kh * p.group + h_in] * 1.4426950408889634f - m_ref) : 0.f;
+            const float inv = l_run > 0.f ? 1.f / (l_run + extra) : 0.f;
             __nv_bfloat16* dst = p.out + (size_t)(q_start + tok0 + t_in) * p.out_stride +
                                  (size_t)(kh * p.group + h_in) * AT_HD + 64 * part;
 #pragma unroll
@@ -649,8 +661,9 @@ int at_make_map(CUtensorMap* map, const void* base, int rank, const cuuint64_t* 
 // tokens_per_tile = 128 / group tokens of that sequence. q: [n_tokens][q_stride] with query head h
 // at column h * 128. cache: [n_pages][2][kv heads][page_size * 128], keys [slot][dim], values
 // [dim][slot]. Every token of every listed sequence must be covered by tiles.
-extern "C" int mx_attention_merge_bf16(const float* part_o, const float* part_ml, void* out, int out_stride,
-                                       int n_tokens, int n_heads, int head_dim, int n_splits, cudaStream_t stream);
+extern "C" int mx_attention_merge_bf16_sink(const float* part_o, const float* part_ml, void* out, int out_stride,
+                                            int n_tokens, int n_heads, int head_dim, int n_splits, const float* sink,
+                                            cudaStream_t stream);
 
 // n_splits > 1: every tile's keys are shared out between n_splits blocks, whose partial results go to
 // `scratch` ((tokens x heads x splits) x (128 + 2) floats) and are merged by mx_attention_merge_bf16.
@@ -659,7 +672,7 @@ extern "C" int mx_paged_attention_tc_split(const void* q, int q_stride, const vo
                                            const int* context_lens, const int* tiles, int n_tiles, int n_tokens,
                                            int n_heads, int n_kv_heads, int head_dim, int window, float scale,
                                            void* out, int out_stride, int n_splits, float* scratch, int* status,
-                                           cudaStream_t stream) {
+                                           float softcap, const float* sink, cudaStream_t stream) {
     if (n_tiles <= 0 || n_tokens <= 0) return MX_OK;
     if (n_splits < 1 || n_splits > 64) MX_REFUSE("tcgen05 attention: %d key splits", n_splits);
     if (n_splits > 1 && scratch == nullptr) MX_REFUSE("tcgen05 attention: key splits without scratch memory");
@@ -707,6 +720,9 @@ extern "C" int mx_paged_attention_tc_split(const void* q, int q_stride, const vo
     p.bt_stride = bt_stride; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.group = group;
     p.tokens_per_tile = tokens_per_tile; p.page_size = page_size; p.page_shift = page_size == 16 ? 4 : 5;
     p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
+    p.cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
+    p.cap_in = softcap > 0.f ? scale / softcap : 0.f;
+    p.sink = sink;
     p.n_splits = n_splits;
     p.part_o = scratch;
     p.part_ml = scratch ? scratch + (size_t)n_tokens * n_heads * n_splits * AT_HD : nullptr;
@@ -720,7 +736,8 @@ extern "C" int mx_paged_attention_tc_split(const void* q, int q_stride, const vo
     attention_tc_kernel<<<dim3(n_tiles, n_kv_heads, n_splits), AT_THREADS, smem, stream>>>(q_map, k_map, v_map, p);
     const int rc = mx_launch_status();
     if (rc != MX_OK || n_splits == 1) return rc;
-    return mx_attention_merge_bf16(p.part_o, p.part_ml, out, out_stride, n_tokens, n_heads, AT_HD, n_splits, stream);
+    return mx_attention_merge_bf16_sink(p.part_o, p.part_ml, out, out_stride, n_tokens, n_heads, AT_HD, n_splits, sink,
+                                        stream);
 }
 
 extern "C" int mx_paged_attention_tc(const void* q, int q_stride, const void* cache, long long n_pages,
@@ -730,5 +747,5 @@ extern "C" int mx_paged_attention_tc(const void* q, int q_stride, const void* ca
                                      void* out, int out_stride, int* status, cudaStream_t stream) {
     return mx_paged_attention_tc_split(q, q_stride, cache, n_pages, page_size, block_tables, bt_stride, cu_q,
                                        context_lens, tiles, n_tiles, n_tokens, n_heads, n_kv_heads, head_dim, window,
-                                       scale, out, out_stride, 1, nullptr, status, stream);
+                                       scale, out, out_stride, 1, nullptr, status, 0.f, nullptr, stream);
 }

@@ -115,6 +115,15 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return total;
 }
 
+// tanh from one ex2 and one reciprocal: 1 - 2 / (1 + e^(2x)), absolute error of a few 1e-7; for scores that are
+// capped in float inside the tensor-core attention kernels (tanh.approx is good to 2^-11 only).
+__device__ __forceinline__ float tanh_by_exp2(float x) {
+    x = fminf(fmaxf(x, -15.f), 15.f);
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(e) : "f"(x * 2.885390081777927f));
+    return 1.f - __fdividef(2.f, 1.f + e);
+}
+
 // tanh-approximated GELU: 0.5 u (1 + tanh(sqrt(2/pi) (u + 0.044715 u^3))).
 __device__ __forceinline__ float gelu_tanh(float u) {
     const float k0 = 0.7978845608028654f, k1 = 0.044715f;

@@ -1,0 +1,320 @@
+// A routed feed-forward: every token runs `top` of `experts` small gated feed-forwards.
+//
+// mx_moe_route: per token the router's logits z = R h on the FP32 cores (R float [experts][K]), scores
+//   s = sigmoid(z), and the choice: the experts form `n_groups` runs of neighbours, a run is worth the sum of its
+//   two largest scores, only the `keep` best runs may supply experts, and of those the `top` largest scores win
+//   (ties go to the lower index). The weights are the winners' scores over their sum (+ 1e-20) times `scale`.
+//   The kernel also counts the pairs of every expert and gives each (token, slot) pair its place among its
+//   expert's pairs (the order inside an expert is whatever the atomics make it: every row of a grouped product
+//   depends on that row alone, so the order changes no number).
+// mx_moe_plan (one block): from the counts, the first sorted row of every expert and the list of row tiles
+//   (expert, first sorted row, rows) that the grouped products walk; the number of tiles stays on the device.
+// mx_moe_scatter: order[first[e] + place] = pair: the pairs sorted by expert.
+// mx_moe_gemm: the grouped product over the sorted rows, a block per (row tile, column tile), on the FP32 cores
+//   with float accumulators (operands float or bfloat16). GLU form: rows gathered from the tokens' activations,
+//   two accumulators (gate rows and up rows of the expert's stacked matrix), out = act(gate) * up in the operand
+//   type. Plain form: rows are the sorted rows themselves, out[pair] = weight[pair] * product in float, one row per
+//   pair, so that the sum over a token's pairs can be formed in a fixed order.
+// mx_moe_combine: residual[t] += sum over the token's pairs, slot 0 first.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int MOE_BM = 32, MOE_BN = 64, MOE_BK = 16;
+
+__device__ __forceinline__ void arg_best(float& v, int& i) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float v2 = __shfl_xor_sync(0xffffffffu, v, o);
+        const int i2 = __shfl_xor_sync(0xffffffffu, i, o);
+        if (v2 > v || (v2 == v && i2 < i)) { v = v2; i = i2; }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const T* __restrict__ h, int ld, const float* __restrict__ router, int K, int n_experts, int top,
+                 int n_groups, int keep, float scale, int* __restrict__ ids, float* __restrict__ weights,
+                 int* __restrict__ counts, int* __restrict__ place) {
+    extern __shared__ float route_s[];
+    float* h_s = route_s;                         // [K]
+    float* score = h_s + K;                       // [experts]
+    float* open = score + n_experts;              // [experts]: the score while the expert may still be chosen, else -1
+    float* worth = open + n_experts;              // [groups]
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int k = tid; k < K; k += blockDim.x) h_s[k] = to_float(h[(size_t)t * ld + k]);
+    __syncthreads();
+    for (int e = warp; e < n_experts; e += blockDim.x >> 5) {
+        const float* w = router + (size_t)e * K;
+        float z = 0.f;
+        for (int k = lane; k < K; k += 32) z = fmaf(w[k], h_s[k], z);
+        z = warp_sum(z);
+        if (lane == 0) score[e] = 1.0f / (1.0f + expf(-z));
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    const int per = n_experts / n_groups;
+    const bool limited = n_groups > 1 && keep < n_groups;
+    for (int g = lane; g < n_groups; g += 32) {
+        float a = -1.f, b = -1.f;                 // the two largest of the run (scores are positive)
+        for (int e = g * per; e < (g + 1) * per; ++e) {
+            const float s = score[e];
+            if (s > a) { b = a; a = s; } else if (s > b) { b = s; }
+        }
+        worth[g] = a + (per > 1 ? b : 0.f);
+    }
+    for (int e = lane; e < n_experts; e += 32) open[e] = limited ? -1.f : score[e];
+    __syncwarp();
+    if (limited) {
+        for (int round = 0; round < keep; ++round) {
+            float v = -2.f;
+            int i = 0x7fffffff;
+            for (int g = lane; g < n_groups; g += 32)
+                if (worth[g] > v) { v = worth[g]; i = g; }
+            arg_best(v, i);
+            __syncwarp();
+            if (lane == 0) worth[i] = -3.f;
+            for (int e = i * per + lane; e < (i + 1) * per; e += 32) open[e] = score[e];
+            __syncwarp();
+        }
+    }
+    float total = 0.f, mine = 0.f;
+    int my_id = 0;
+    for (int slot = 0; slot < top; ++slot) {
+        float v = -2.f;
+        int i = 0x7fffffff;
+        for (int e = lane; e < n_experts; e += 32)
+            if (open[e] > v) { v = open[e]; i = e; }
+        arg_best(v, i);
+        __syncwarp();
+        if (lane == 0) open[i] = -3.f;
+        __syncwarp();
+        total += v;
+        if (lane == slot % 32 && slot / 32 == 0) { mine = v; my_id = i; }
+        if (slot >= 32 && lane == 0) {            // more slots than lanes: written one by one
+            ids[(size_t)t * top + slot] = i;
+            weights[(size_t)t * top + slot] = v;  // normalised below
+            place[(size_t)t * top + slot] = atomicAdd(&counts[i], 1);
+        }
+    }
+    const float norm = scale / (total + 1e-20f);
+    if (lane < min(top, 32)) {
+        ids[(size_t)t * top + lane] = my_id;
+        weights[(size_t)t * top + lane] = mine * norm;
+        place[(size_t)t * top + lane] = atomicAdd(&counts[my_id], 1);
+    }
+    __syncwarp();
+    if (lane == 0)
+        for (int slot = 32; slot < top; ++slot) weights[(size_t)t * top + slot] *= norm;
+}
+
+__global__ void moe_plan_kernel(const int* __restrict__ counts, int n_experts, int* __restrict__ first,
+                                int* __restrict__ tile_map, int* __restrict__ n_tiles) {
+    extern __shared__ int plan_s[];               // [experts + 1]: first tile of every expert
+    if (threadIdx.x == 0) {
+        int rows = 0, tiles = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            first[e] = rows;
+            plan_s[e] = tiles;
+            rows += counts[e];
+            tiles += (counts[e] + MOE_BM - 1) / MOE_BM;
+        }
+        first[n_experts] = rows;
+        plan_s[n_experts] = tiles;
+        n_tiles[0] = tiles;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+        const int count = counts[e], row0 = first[e];
+        for (int i = 0, tile = plan_s[e]; i * MOE_BM < count; ++i, ++tile) {
+            tile_map[3 * tile] = e;
+            tile_map[3 * tile + 1] = row0 + i * MOE_BM;
+            tile_map[3 * tile + 2] = min(MOE_BM, count - i * MOE_BM);
+        }
+    }
+}
+
+__global__ void moe_scatter_kernel(const int* __restrict__ ids, const int* __restrict__ place,
+                                   const int* __restrict__ first, int* __restrict__ order, int n_pairs) {
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p < n_pairs) order[first[ids[p]] + place[p]] = p;
+}
+
+__device__ __forceinline__ float act_silu(float g) { return g / (1.0f + expf(-g)); }
+
+// ACT: 0 = gelu (tanh form), 1 = silu
+template <typename T, bool GLU, int ACT>
+__global__ void __launch_bounds__(256)
+moe_gemm_kernel(const T* __restrict__ a, int lda, const int* __restrict__ order, int a_div, const T* __restrict__ w,
+                long long expert_stride, int N, int K, const int* __restrict__ tile_map,
+                const int* __restrict__ n_tiles, void* __restrict__ out_raw, const float* __restrict__ pair_weight) {
+    if ((int)blockIdx.y >= n_tiles[0]) return;
+    __shared__ float a_s[MOE_BK][MOE_BM + 1], w_s[MOE_BK][MOE_BN + 1], u_s[GLU ? MOE_BK : 1][MOE_BN + 1];
+    __shared__ int src_row[MOE_BM];
+    const int expert = tile_map[3 * blockIdx.y], row0 = tile_map[3 * blockIdx.y + 1], rows = tile_map[3 * blockIdx.y + 2];
+    const int n0 = blockIdx.x * MOE_BN, tid = threadIdx.x;
+    if (tid < MOE_BM) src_row[tid] = tid < rows ? (GLU ? order[row0 + tid] / a_div : row0 + tid) : -1;
+    __syncthreads();
+    const T* we = w + (size_t)expert * expert_stride;
+    const int tx = tid & 15, ty = tid >> 4;                   // 4 columns, 2 rows a thread
+    float acc[2][4] = {}, acc_u[2][4] = {};
+    const int a_row = tid >> 3, a_k = (tid & 7) * 2;          // this thread's two elements of the row tile
+    const int w_row = tid >> 2, w_k = (tid & 3) * 4;          // ... and four of each weight tile
+    for (int k0 = 0; k0 < K; k0 += MOE_BK) {
+        {
+            const int r = src_row[a_row];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int k = k0 + a_k + e;
+                a_s[a_k + e][a_row] = (r >= 0 && k < K) ? to_float(a[(size_t)r * lda + k]) : 0.f;
+            }
+            const int n = n0 + w_row;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int k = k0 + w_k + e;
+                const bool ok = n < N && k < K;
+                w_s[w_k + e][w_row] = ok ? to_float(we[(size_t)n * K + k]) : 0.f;
+                if (GLU) u_s[w_k + e][w_row] = ok ? to_float(we[(size_t)(N + n) * K + k]) : 0.f;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < MOE_BK; ++k) {
+            const float a0 = a_s[k][2 * ty], a1 = a_s[k][2 * ty + 1];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float wv = w_s[k][4 * tx + c];
+                acc[0][c] = fmaf(a0, wv, acc[0][c]);
+                acc[1][c] = fmaf(a1, wv, acc[1][c]);
+                if (GLU) {
+                    const float uv = u_s[k][4 * tx + c];
+                    acc_u[0][c] = fmaf(a0, uv, acc_u[0][c]);
+                    acc_u[1][c] = fmaf(a1, uv, acc_u[1][c]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = 2 * ty + r;
+        if (row >= rows) continue;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int n = n0 + 4 * tx + c;
+            if (n >= N) continue;
+            if (GLU) {
+                const float g = acc[r][c];
+                const float act = ACT == 0 ? gelu_tanh(g) : act_silu(g);
+                reinterpret_cast<T*>(out_raw)[(size_t)(row0 + row) * N + n] = from_float<T>(act * acc_u[r][c]);
+            } else {
+                const int pair = order[row0 + row];
+                reinterpret_cast<float*>(out_raw)[(size_t)pair * N + n] = acc[r][c] * pair_weight[pair];
+            }
+        }
+    }
+}
+
+__global__ void moe_combine_kernel(const float* __restrict__ pairs, float* __restrict__ residual, int top, int width,
+                                   long long count) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const long long t = i / width;
+    const int c = (int)(i - t * width);
+    float sum = 0.f;
+    for (int s = 0; s < top; ++s) sum += pairs[((size_t)t * top + s) * width + c];
+    residual[i] += sum;
+}
+
+template <typename T>
+__global__ void glu_kernel(const T* __restrict__ gu, int ld, T* __restrict__ out, int ff, int act, long long count) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const long long t = i / ff;
+    const int c = (int)(i - t * ff);
+    const float g = to_float(gu[(size_t)t * ld + c]);
+    const float u = to_float(gu[(size_t)t * ld + ff + c]);
+    out[i] = from_float<T>((act == 0 ? gelu_tanh(g) : act_silu(g)) * u);
+}
+
+}  // namespace
+
+extern "C" int mx_moe_route(const void* h, int dtype, int ld, const float* router, int K, int n_experts, int top,
+                            int n_groups, int keep, float scale, int* ids, float* weights, int* counts, int* place,
+                            int n_tokens, cudaStream_t stream) {
+    if (n_tokens <= 0) return MX_OK;
+    if (n_experts <= 0 || top <= 0 || top > n_experts) MX_REFUSE("router: top %d of %d experts", top, n_experts);
+    if (n_groups <= 0 || n_experts % n_groups != 0) MX_REFUSE("router: %d experts in %d equal groups", n_experts, n_groups);
+    if (keep <= 0 || keep > n_groups) MX_REFUSE("router: %d of %d groups kept", keep, n_groups);
+    if (keep * (n_experts / n_groups) < top) MX_REFUSE("router: %d kept groups hold fewer than %d experts", keep, top);
+    const size_t smem = ((size_t)K + 2 * (size_t)n_experts + n_groups) * sizeof(float);
+    if (smem > 48 * 1024) MX_REFUSE("router: %zu bytes of shared memory for K = %d and %d experts", smem, K, n_experts);
+    if (dtype == MX_DTYPE_F32)
+        moe_route_kernel<float><<<n_tokens, 128, smem, stream>>>((const float*)h, ld, router, K, n_experts, top, n_groups,
+                                                                keep, scale, ids, weights, counts, place);
+    else
+        moe_route_kernel<__nv_bfloat16><<<n_tokens, 128, smem, stream>>>((const __nv_bfloat16*)h, ld, router, K, n_experts,
+                                                                        top, n_groups, keep, scale, ids, weights, counts,
+                                                                        place);
+    return mx_launch_status();
+}
+
+extern "C" int mx_moe_tile_rows() { return MOE_BM; }
+
+extern "C" int mx_moe_plan(const int* counts, const int* ids, const int* place, int n_experts, int n_pairs, int* first,
+                           int* tile_map, int* n_tiles, int* order, cudaStream_t stream) {
+    if (n_pairs <= 0) return MX_OK;
+    if (n_experts > 8192) MX_REFUSE("routed feed-forward: %d experts", n_experts);
+    moe_plan_kernel<<<1, 256, (size_t)(n_experts + 1) * sizeof(int), stream>>>(counts, n_experts, first, tile_map, n_tiles);
+    int rc = mx_launch_status();
+    if (rc != MX_OK) return rc;
+    moe_scatter_kernel<<<(n_pairs + 255) / 256, 256, 0, stream>>>(ids, place, first, order, n_pairs);
+    return mx_launch_status();
+}
+
+// glu != 0: a = the tokens' activations [tokens][lda], source row of sorted row r is order[r] / a_div, w holds per
+// expert 2 N rows (gate, then up), out [pairs][N] in the operand type by sorted row. glu == 0: a = [pairs][lda] by
+// sorted row, out float [pairs][N] by pair, times pair_weight. `max_tiles` bounds the tiles a step can have.
+extern "C" int mx_moe_gemm(const void* a, int dtype, int lda, const int* order, int a_div, const void* w,
+                           long long expert_stride, int N, int K, const int* tile_map, const int* n_tiles, int max_tiles,
+                           void* out, const float* pair_weight, int glu, int act, cudaStream_t stream) {
+    if (max_tiles <= 0 || N <= 0) return MX_OK;
+    if (max_tiles > 65535) MX_REFUSE("routed feed-forward: %d row tiles exceed the grid", max_tiles);
+    const dim3 grid((N + MOE_BN - 1) / MOE_BN, max_tiles);
+#define MOE_LAUNCH(T, GLU, ACT)                                                                                        \
+    moe_gemm_kernel<T, GLU, ACT><<<grid, 256, 0, stream>>>((const T*)a, lda, order, a_div, (const T*)w, expert_stride, \
+                                                           N, K, tile_map, n_tiles, out, pair_weight)
+    if (dtype == MX_DTYPE_F32) {
+        if (!glu) MOE_LAUNCH(float, false, 0);
+        else if (act == 0) MOE_LAUNCH(float, true, 0);
+        else MOE_LAUNCH(float, true, 1);
+    } else {
+        if (!glu) MOE_LAUNCH(__nv_bfloat16, false, 0);
+        else if (act == 0) MOE_LAUNCH(__nv_bfloat16, true, 0);
+        else MOE_LAUNCH(__nv_bfloat16, true, 1);
+    }
+#undef MOE_LAUNCH
+    return mx_launch_status();
+}
+
+extern "C" int mx_moe_combine(const float* pairs, float* residual, int n_tokens, int top, int width, cudaStream_t stream) {
+    const long long count = (long long)n_tokens * width;
+    if (count <= 0) return MX_OK;
+    moe_combine_kernel<<<(unsigned)((count + 255) / 256), 256, 0, stream>>>(pairs, residual, top, width, count);
+    return mx_launch_status();
+}
+
+// out = act(gate) * up on rows [gate (ff) | up (ff)]; act 0 = gelu (tanh form), 1 = silu
+extern "C" int mx_glu(const void* gu, int ld, void* out, int dtype, int n_tokens, int ff, int act, cudaStream_t stream) {
+    const long long count = (long long)n_tokens * ff;
+    if (count <= 0) return MX_OK;
+    const unsigned blocks = (unsigned)((count + 255) / 256);
+    if (dtype == MX_DTYPE_F32)
+        glu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, ld, (float*)out, ff, act, count);
+    else
+        glu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, ld, (__nv_bfloat16*)out, ff, act,
+                                                             count);
+    return mx_launch_status();
+}

@@ -60,7 +60,12 @@ def load_model(model_dir: str | Path, dtype="bfloat16", device="cuda:0", page_si
                gemm_backend: str = "auto"):
     """(config, model) from a folder with config.json and model.safetensors."""
     config = load_config(model_dir)
-    model = build_model(config, ModelFiles(model_dir), dtype, device, page_size, gemm_backend)
+    files = ModelFiles(model_dir)
+    if hasattr(config, "with_tensor_shapes"):
+        # sizes that config.json leaves to the tensors (the rank of a low-rank map, for one)
+        present = set(files.names())
+        config = config.with_tensor_shapes(lambda name: files.shape(name) if name in present else None)
+    model = build_model(config, files, dtype, device, page_size, gemm_backend)
     return config, model
 
 

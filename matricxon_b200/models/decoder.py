@@ -166,7 +166,9 @@ class DecoderModel:
                     x = x.tensor()
                 x = layer.forward(x, ctx, self.bindings[position])
                 if taps is not None:        # a caller that wants the stream after every schedule entry
-                    taps.append((x.tensor() if isinstance(x, PendingSum) else x).clone())
+                    if isinstance(x, PendingSum):
+                        x = x.tensor()      # added up here and now: the next norm must not add it again
+                    taps.append(x.clone())
         finally:
             ctx.pending_sum_wanted = False
         return x.tensor() if isinstance(x, PendingSum) else x      # the last block's sum, added up here

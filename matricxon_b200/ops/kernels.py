@@ -360,6 +360,14 @@ def gemm_skinny_rope(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None
     _launched()
 
 
+def _sink_ptr(sink: torch.Tensor | None, n_heads: int) -> int | None:
+    if sink is None:
+        return None
+    _need(sink, "sink", torch.float32)
+    assert sink.numel() == n_heads, (sink.shape, n_heads)
+    return sink.data_ptr()
+
+
 def attention_scratch_bytes(n_tokens: int, n_heads: int, head_dim: int, n_splits: int) -> int:
     return int(library().mx_attention_scratch_bytes(n_tokens, n_heads, head_dim, n_splits))
 
@@ -368,11 +376,14 @@ def paged_attention(q: torch.Tensor, q_stride: int, cache: torch.Tensor, block_t
                     tok_seq: torch.Tensor, positions: torch.Tensor, n_tokens: int, n_heads: int,
                     n_kv_heads: int, head_dim: int, window: int | None, scale: float,
                     out: torch.Tensor, status: torch.Tensor, n_splits: int = 1,
-                    scratch: torch.Tensor | None = None) -> None:
+                    scratch: torch.Tensor | None = None, softcap: float | None = None,
+                    sink: torch.Tensor | None = None) -> None:
     """Attention of ``n_tokens`` query rows over the paged cache.
 
     ``q`` points at the first query head of row 0 and rows are ``q_stride`` elements apart
     (so the q part of a fused qkv buffer can be used in place). ``out`` is [tokens, heads * dim].
+    ``softcap``: scaled scores become ``softcap * tanh(score / softcap)``. ``sink`` (float32, one per
+    head): ``exp(sink[h])`` joins the softmax's denominator and brings no value.
     """
     _need(q, "q", contiguous=False)
     _need(cache, "cache", q.dtype)
@@ -393,7 +404,8 @@ def paged_attention(q: torch.Tensor, q_stride: int, cache: torch.Tensor, block_t
         _ptr(q), dtype_code(q.dtype), q_stride, _ptr(cache), cache.shape[0], page_size,
         _ptr(block_tables), block_tables.stride(0), _ptr(tok_seq), _ptr(positions), n_tokens,
         n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), _ptr(out), out.stride(0),
-        n_splits, _ptr(scratch), _ptr(status), _stream()), "paged_attention")
+        n_splits, _ptr(scratch), _ptr(status), float(softcap or 0.0), _sink_ptr(sink, n_heads), _stream()),
+        "paged_attention")
     _launched(2 if n_splits > 1 else 1)
 
 
@@ -434,7 +446,8 @@ def paged_attention_tc(q: torch.Tensor, q_stride: int, cache: torch.Tensor, bloc
                        cu_q: torch.Tensor, context_lens: torch.Tensor, tiles: torch.Tensor, n_tiles: int,
                        n_tokens: int, n_heads: int, n_kv_heads: int, head_dim: int, window: int | None,
                        scale: float, out: torch.Tensor, status: torch.Tensor, n_splits: int = 1,
-                       scratch: torch.Tensor | None = None) -> None:
+                       scratch: torch.Tensor | None = None, softcap: float | None = None,
+                       sink: torch.Tensor | None = None) -> None:
     """Attention of prompt portions on tcgen05 (bfloat16, head_dim 128, pages of 16 or 32).
     ``tiles`` is int32 [n_tiles, 2]: (sequence, first token) of tiles of 128 // group tokens
     (``attention_tile_lists(..., token_tiles=True)``); ``q`` holds the step's rows, query head h
@@ -457,8 +470,8 @@ def paged_attention_tc(q: torch.Tensor, q_stride: int, cache: torch.Tensor, bloc
         _ptr(q), q_stride, _ptr(cache), cache.shape[0], page_size, _ptr(block_tables),
         block_tables.stride(0), _ptr(cu_q), _ptr(context_lens), _ptr(tiles), n_tiles, n_tokens,
         n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), _ptr(out), out.stride(0),
-        int(n_splits), _ptr(scratch) if n_splits > 1 else None, _ptr(status), _stream()),
-        "paged_attention_tc")
+        int(n_splits), _ptr(scratch) if n_splits > 1 else None, _ptr(status), float(softcap or 0.0),
+        _sink_ptr(sink, n_heads), _stream()), "paged_attention_tc")
     _launched()
 
 
@@ -467,7 +480,8 @@ def paged_attention_mma(q: torch.Tensor, q_stride: int, cache: torch.Tensor,
                         tiles: torch.Tensor, n_tiles: int, narrow: bool, n_tokens: int, n_heads: int,
                         n_kv_heads: int, head_dim: int, window: int | None, scale: float,
                         out: torch.Tensor, status: torch.Tensor, n_splits: int = 1,
-                        scratch: torch.Tensor | None = None) -> None:
+                        scratch: torch.Tensor | None = None, softcap: float | None = None,
+                        sink: torch.Tensor | None = None) -> None:
     """Tensor-core attention (bfloat16, head_dim 64 or 128). ``tiles`` is int32 [n_tiles, 2]:
     (sequence, first row) of each tile of the (token, head-in-group) rows; ``narrow`` tiles
     hold at most 16 rows, the others 64 (see ``attention_tile_lists``)."""
@@ -495,8 +509,8 @@ def paged_attention_mma(q: torch.Tensor, q_stride: int, cache: torch.Tensor,
         _ptr(q), q_stride, _ptr(cache), cache.shape[0], page_size, _ptr(block_tables),
         block_tables.stride(0), _ptr(cu_q), _ptr(context_lens), _ptr(tiles) if tiles is not None else None, n_tiles,
         1 if narrow else 0, n_tokens, n_heads, n_kv_heads, head_dim, int(window or 0), float(scale),
-        _ptr(out), out.stride(0), n_splits, _ptr(scratch), _ptr(status), _stream()),
-        "paged_attention_mma")
+        _ptr(out), out.stride(0), n_splits, _ptr(scratch), _ptr(status), float(softcap or 0.0),
+        _sink_ptr(sink, n_heads), _stream()), "paged_attention_mma")
     _launched(2 if n_splits > 1 else 1)
 
 
@@ -847,3 +861,232 @@ def rglru_scan_chunked(xy: torch.Tensor, x_col: int, y_col: int, u: torch.Tensor
                                           _ptr(scratch), _ptr(out), dtype_code(out.dtype), n_seqs, width,
                                           block_width, taps, _stream()), "rglru_scan_chunked")
     _launched(3)
+
+
+# ---------------------------------------------------------------------- dynamic tanh
+def dyt(x: torch.Tensor, weight: torch.Tensor, shift: torch.Tensor | None, alpha: torch.Tensor, out: torch.Tensor,
+        rows: torch.Tensor | None = None, acc: torch.Tensor | None = None,
+        col_bias: torch.Tensor | None = None) -> None:
+    """out[r] = tanh(alpha * x[row]) * weight + shift, row = rows[r] if given else r; ``alpha`` is a float32
+    scalar on the device. With ``acc`` (float32, the shape of x): ``x += acc + col_bias`` first, written back."""
+    _need(x, "x", torch.float32)
+    _need(weight, "weight", torch.float32)
+    _need(alpha, "alpha", torch.float32)
+    _need(out, "out")
+    n_rows, hidden = out.shape
+    assert x.shape[1] == hidden and weight.numel() == hidden and alpha.numel() == 1
+    assert (rows.numel() if rows is not None else x.shape[0]) == n_rows
+    if shift is not None:
+        _need(shift, "shift", torch.float32)
+        assert shift.numel() == hidden
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    if acc is not None:
+        _need(acc, "acc", torch.float32)
+        assert acc.shape == x.shape and rows is None
+        if col_bias is not None:
+            _need(col_bias, "col_bias", torch.float32)
+    check(library().mx_dyt(_ptr(x), _ptr(rows), _ptr(acc), _ptr(col_bias) if acc is not None else None, _ptr(weight),
+                           _ptr(shift), _ptr(alpha), _ptr(out), dtype_code(out.dtype), n_rows, hidden, _stream()), "dyt")
+    _launched()
+
+
+# ---------------------------------------------------------------------- partly rotated, blended, head-gated attention
+def rotate_mix_kv_write(proj: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor, rot: int,
+                        other: torch.Tensor | None, mix: torch.Tensor | None, slots: torch.Tensor | None,
+                        cache: torch.Tensor | None, q_out: torch.Tensor, n_heads: int, n_kv_heads: int, dim: int,
+                        vdim: int, status: torch.Tensor) -> None:
+    """From the float rows ``[heads x dim | kv heads x dim | kv heads x vdim | ...]`` of a fused projection: queries
+    with their first ``rot`` entries rotated (pairs (i, i + rot/2), angle ``position * freq[i]``) to ``q_out``
+    [tokens, heads * hd], keys rotated the same way and values to ``slots`` of ``cache``
+    [pages, 2, kv heads, page_size, hd]; hd >= dim, vdim, tails are zero. ``other`` (a float32 view
+    [tokens, kv heads * vdim], any row stride) and ``mix`` (a float32 scalar on the device): the stored values are
+    ``(1 - mix) * v + mix * other``."""
+    _need(proj, "proj", torch.float32)
+    _need(positions, "positions", torch.int32)
+    _need(freq, "freq", torch.float32)
+    _need(q_out, "q_out")
+    n = proj.shape[0]
+    hd = q_out.shape[1] // n_heads
+    assert tuple(q_out.shape) == (n, n_heads * hd) and freq.numel() == rot // 2
+    other_ld = 0
+    if other is not None:
+        _need(other, "other", torch.float32, contiguous=False)
+        _need(mix, "mix", torch.float32)
+        assert tuple(other.shape) == (n, n_kv_heads * vdim) and other.stride(1) == 1 and mix.numel() == 1
+        other_ld = other.stride(0)
+    n_pages = page_size = 0
+    if cache is not None:
+        _need(cache, "cache", q_out.dtype)
+        _need(slots, "slots", torch.int32)
+        assert tuple(cache.shape[1:3]) == (2, n_kv_heads) and cache.shape[4] == hd, cache.shape
+        n_pages, page_size = cache.shape[0], cache.shape[3]
+    check(library().mx_rotate_mix_kv_write(_ptr(proj), proj.stride(0), _ptr(positions), _ptr(freq), rot, _ptr(other),
+                                           other_ld, _ptr(mix) if other is not None else None, _ptr(slots), _ptr(cache),
+                                           n_pages, page_size, _ptr(q_out), dtype_code(q_out.dtype), n, n_heads,
+                                           n_kv_heads, dim, vdim, hd, _ptr(status), _stream()), "rotate_mix_kv_write")
+    _launched()
+
+
+def head_gate(attn: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, n_heads: int, vdim: int) -> None:
+    """out[t, h * vdim + e] = attn[t, h * hd + e] * sigmoid(gate[t, h]); ``gate`` is a float32 view [tokens, heads]
+    with any row stride."""
+    _need(attn, "attn")
+    _need(gate, "gate", torch.float32, contiguous=False)
+    _need(out, "out", attn.dtype)
+    n = attn.shape[0]
+    hd = attn.shape[1] // n_heads
+    assert tuple(out.shape) == (n, n_heads * vdim) and tuple(gate.shape) == (n, n_heads) and gate.stride(1) == 1
+    check(library().mx_head_gate(_ptr(attn), _ptr(gate), gate.stride(0), _ptr(out), dtype_code(attn.dtype), n, n_heads,
+                                 vdim, hd, _stream()), "head_gate")
+    _launched()
+
+
+# ---------------------------------------------------------------------- gated linear attention
+def gla_decay(low: torch.Tensor, a2: torch.Tensor, bias: torch.Tensor | None, tau: float, decay: torch.Tensor) -> None:
+    """decay[t, c] = sigmoid(a2[c] . low[t] + bias[c]) ** (1 / tau), all float32; ``low`` [tokens, rank] may be a
+    column range of wider rows."""
+    _need(low, "low", torch.float32, contiguous=False)
+    _need(a2, "a2", torch.float32)
+    _need(decay, "decay", torch.float32)
+    n, rank = low.shape
+    channels = a2.shape[0]
+    assert tuple(a2.shape) == (channels, rank) and tuple(decay.shape) == (n, channels) and low.stride(1) == 1
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        assert bias.numel() == channels
+    check(library().mx_gla_decay(_ptr(low), low.stride(0), _ptr(a2), _ptr(bias), float(tau), _ptr(decay), n, channels,
+                                 rank, _stream()), "gla_decay")
+    _launched()
+
+
+def gla_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, q_scale: float,
+             state: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor, n_seqs: int, out: torch.Tensor,
+             n_heads: int, dim: int, vdim: int) -> None:
+    """``S <- diag(decay_t) S + k_t v_t^T; out_t = S^T (q_scale * q_t)`` over every sequence's tokens in order, from
+    and to ``state`` [slots, heads, dim, vdim] (float32); q, k and v are column ranges of the float rows ``proj``."""
+    for name, tensor in (("proj", proj), ("decay", decay), ("state", state), ("out", out)):
+        _need(tensor, name, torch.float32)
+    n = proj.shape[0]
+    assert tuple(state.shape[1:]) == (n_heads, dim, vdim), state.shape
+    assert tuple(decay.shape) == (n, n_heads * dim) and tuple(out.shape) == (n, n_heads * vdim)
+    check(library().mx_gla_scan(_ptr(proj), proj.stride(0), q_col, k_col, v_col, _ptr(decay), float(q_scale),
+                                _ptr(state), _ptr(cu_q), _ptr(state_slots), _ptr(out), n_seqs, n_heads, dim, vdim,
+                                _stream()), "gla_scan")
+    _launched()
+
+
+def gla_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                  n_heads: int, vdim: int) -> None:
+    """out[t, h, e] = unit(o[t, h])[e] * weight[e] * silu(gate[t, h, e]); unit is the RMS norm over one head's
+    ``vdim`` entries with eps inside the root; ``gate`` a float32 view with any row stride."""
+    _need(o, "o", torch.float32)
+    _need(gate, "gate", torch.float32, contiguous=False)
+    _need(weight, "weight", torch.float32)
+    _need(out, "out")
+    n = o.shape[0]
+    assert tuple(o.shape) == (n, n_heads * vdim) and tuple(gate.shape) == (n, n_heads * vdim) and gate.stride(1) == 1
+    assert tuple(out.shape) == (n, n_heads * vdim) and weight.numel() == vdim
+    check(library().mx_gla_norm_gate(_ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), float(eps), _ptr(out),
+                                     dtype_code(out.dtype), n, n_heads, vdim, _stream()), "gla_norm_gate")
+    _launched()
+
+
+# ---------------------------------------------------------------------- gated and routed feed-forwards
+GLU_ACTIVATIONS = {"gelu_tanh": 0, "silu": 1}
+
+
+def glu(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> None:
+    """Rows ``[gate | up]`` -> ``act(gate) * up``."""
+    _need(gate_up, "gate_up")
+    _need(out, "out", gate_up.dtype)
+    n, ff = out.shape
+    assert tuple(gate_up.shape) == (n, 2 * ff)
+    check(library().mx_glu(_ptr(gate_up), gate_up.stride(0), _ptr(out), dtype_code(out.dtype), n, ff,
+                           GLU_ACTIVATIONS[activation], _stream()), "glu")
+    _launched()
+
+
+def moe_tile_rows() -> int:
+    return int(library().mx_moe_tile_rows())
+
+
+def moe_route(h: torch.Tensor, router: torch.Tensor, top: int, n_groups: int, keep: int, scale: float,
+              ids: torch.Tensor, weights: torch.Tensor, counts: torch.Tensor, place: torch.Tensor) -> None:
+    """Per token: sigmoid scores of the float32 router [experts, K], the ``top`` best experts of the ``keep`` best
+    of ``n_groups`` runs of neighbours (a run is worth its two best scores), weights = scores / their sum * scale.
+    ``counts`` [experts] must be zero; afterwards it holds every expert's pairs and ``place`` each pair's index
+    among them."""
+    _need(h, "h")
+    _need(router, "router", torch.float32)
+    for name, tensor in (("ids", ids), ("counts", counts), ("place", place)):
+        _need(tensor, name, torch.int32)
+    _need(weights, "weights", torch.float32)
+    n, k = h.shape
+    n_experts = router.shape[0]
+    assert router.shape[1] == k and ids.numel() == n * top == weights.numel() == place.numel()
+    assert counts.numel() == n_experts
+    check(library().mx_moe_route(_ptr(h), dtype_code(h.dtype), h.stride(0), _ptr(router), k, n_experts, top, n_groups,
+                                 keep, float(scale), _ptr(ids), _ptr(weights), _ptr(counts), _ptr(place), n, _stream()),
+          "moe_route")
+    _launched()
+
+
+def moe_plan(counts: torch.Tensor, ids: torch.Tensor, place: torch.Tensor, first: torch.Tensor, tile_map: torch.Tensor,
+             n_tiles: torch.Tensor, order: torch.Tensor) -> None:
+    """From the routing's counts: ``first`` [experts + 1] (first sorted row of every expert), the row tiles
+    ``tile_map`` [tiles, 3] = (expert, first sorted row, rows) with their number in ``n_tiles`` [1], and
+    ``order`` [pairs]: the pairs sorted by expert."""
+    for name, tensor in (("counts", counts), ("ids", ids), ("place", place), ("first", first), ("tile_map", tile_map),
+                         ("n_tiles", n_tiles), ("order", order)):
+        _need(tensor, name, torch.int32)
+    n_experts, n_pairs = counts.numel(), ids.numel()
+    assert first.numel() == n_experts + 1 and order.numel() == n_pairs
+    assert tile_map.numel() >= 3 * moe_max_tiles(n_pairs, n_experts)
+    check(library().mx_moe_plan(_ptr(counts), _ptr(ids), _ptr(place), n_experts, n_pairs, _ptr(first), _ptr(tile_map),
+                                _ptr(n_tiles), _ptr(order), _stream()), "moe_plan")
+    _launched(2)
+
+
+def moe_max_tiles(n_pairs: int, n_experts: int) -> int:
+    """The most row tiles that ``n_pairs`` pairs shared out between ``n_experts`` experts can make."""
+    rows = moe_tile_rows()
+    return min(n_pairs, n_pairs // rows + n_experts)
+
+
+def moe_gemm(a: torch.Tensor, order: torch.Tensor, a_div: int, w: torch.Tensor, tile_map: torch.Tensor,
+             n_tiles: torch.Tensor, max_tiles: int, out: torch.Tensor, pair_weight: torch.Tensor | None,
+             activation: str | None) -> None:
+    """The grouped product over the pairs sorted by expert. With ``activation``: ``a`` holds the tokens' rows (pair
+    p reads row ``p // a_div``), ``w`` [experts, 2 N, K] stacks gate and up rows, ``out`` [pairs, N] (sorted order,
+    dtype of a) = act(gate) * up. Without: ``a`` [pairs, K] is in sorted order, ``w`` [experts, N, K], ``out``
+    float32 [pairs, N] in pair order = ``pair_weight[pair] *`` product."""
+    _need(a, "a")
+    _need(w, "w", a.dtype)
+    _need(out, "out")
+    for name, tensor in (("order", order), ("tile_map", tile_map), ("n_tiles", n_tiles)):
+        _need(tensor, name, torch.int32)
+    glu_form = activation is not None
+    k = a.shape[1]
+    n = out.shape[1]
+    assert w.shape[2] == k and w.shape[1] == (2 * n if glu_form else n), (a.shape, w.shape, out.shape)
+    if glu_form:
+        assert out.dtype == a.dtype
+    else:
+        _need(pair_weight, "pair_weight", torch.float32)
+        assert out.dtype == torch.float32
+    check(library().mx_moe_gemm(_ptr(a), dtype_code(a.dtype), a.stride(0), _ptr(order), a_div, _ptr(w), w.stride(0), n, k,
+                                _ptr(tile_map), _ptr(n_tiles), max_tiles, _ptr(out), _ptr(pair_weight),
+                                1 if glu_form else 0, GLU_ACTIVATIONS[activation] if glu_form else 0, _stream()),
+          "moe_gemm")
+    _launched()
+
+
+def moe_combine(pairs: torch.Tensor, residual: torch.Tensor, top: int) -> None:
+    """residual[t] += the sum of the token's ``top`` rows of ``pairs`` [tokens * top, width], first slot first."""
+    _need(pairs, "pairs", torch.float32)
+    _need(residual, "residual", torch.float32)
+    n, width = residual.shape
+    assert tuple(pairs.shape) == (n * top, width)
+    check(library().mx_moe_combine(_ptr(pairs), _ptr(residual), n, top, width, _stream()), "moe_combine")
+    _launched()

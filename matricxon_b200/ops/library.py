@@ -41,10 +41,10 @@ _SIGNATURES: dict[str, tuple[list, object]] = {
     "mx_gemm_skinny": ([P, P, P, P, P, I, I, I, I, I, I, I, I, P], I),
     "mx_gemm_skinny_rope": ([P, P, P, P, I, I, I, I, I, P, P, P, P, L, I, I, I, I, P, P], I),
     "mx_attention_scratch_bytes": ([I, I, I, I], L),
-    "mx_paged_attention_mma": ([P, I, P, L, I, P, I, P, P, P, I, I, I, I, I, I, I, F, P, I, I, P, P, P], I),
+    "mx_paged_attention_mma": ([P, I, P, L, I, P, I, P, P, P, I, I, I, I, I, I, I, F, P, I, I, P, P, F, P, P], I),
     "mx_paged_attention_tc": ([P, I, P, L, I, P, I, P, P, P, I, I, I, I, I, I, F, P, I, P, P], I),
-    "mx_paged_attention_tc_split": ([P, I, P, L, I, P, I, P, P, P, I, I, I, I, I, I, F, P, I, I, P, P, P], I),
-    "mx_paged_attention": ([P, I, I, P, L, I, P, I, P, P, I, I, I, I, I, F, P, I, I, P, P, P], I),
+    "mx_paged_attention_tc_split": ([P, I, P, L, I, P, I, P, P, P, I, I, I, I, I, I, F, P, I, I, P, P, F, P, P], I),
+    "mx_paged_attention": ([P, I, I, P, L, I, P, I, P, P, I, I, I, I, I, F, P, I, I, P, P, F, P, P], I),
     "mx_rmsnorm": ([P, P, P, F, P, I, I, I, F, P], I),
     "mx_rmsnorm_sum": ([P, P, F, P, F, P, I, I, I, F, P], I),
     "mx_cast_rows": ([P, P, L, P], I),
@@ -58,6 +58,18 @@ _SIGNATURES: dict[str, tuple[list, object]] = {
     "mx_causal_conv": ([P, I, I, P, P, P, P, P, P, P, P, I, I, I, I, P], I),
     "mx_rglru_scan": ([P, I, I, I, P, P, P, P, F, P, P, P, P, I, I, I, I, I, P], I),
     "mx_rglru_scan_chunked": ([P, I, I, I, P, P, P, P, F, P, P, P, P, P, I, I, P, P, I, I, I, I, I, P], I),
+    "mx_dyt": ([P, P, P, P, P, P, P, P, I, I, I, P], I),
+    "mx_rotate_mix_kv_write": ([P, I, P, P, I, P, I, P, P, P, L, I, P, I, I, I, I, I, I, I, P, P], I),
+    "mx_head_gate": ([P, P, I, P, I, I, I, I, I, P], I),
+    "mx_gla_decay": ([P, I, P, P, F, P, I, I, I, P], I),
+    "mx_gla_scan": ([P, I, I, I, I, P, F, P, P, P, P, I, I, I, I, P], I),
+    "mx_gla_norm_gate": ([P, P, I, P, F, P, I, I, I, I, P], I),
+    "mx_moe_route": ([P, I, I, P, I, I, I, I, I, F, P, P, P, P, I, P], I),
+    "mx_moe_tile_rows": ([], I),
+    "mx_moe_plan": ([P, P, P, I, I, P, P, P, P, P], I),
+    "mx_moe_gemm": ([P, I, I, P, I, P, L, I, I, P, P, I, P, P, I, I, P], I),
+    "mx_moe_combine": ([P, P, I, I, I, P], I),
+    "mx_glu": ([P, I, P, I, I, I, I, P], I),
     "mx_gemm_batched_skinny": ([P, P, P, I, I, I, I, I, I, I, I, L, L, L, P], I),
     "mx_gemm_batched_simt": ([P, P, I, P, P, I, I, I, I, I, I, I, I, L, L, L, L, I, P], I),
 }

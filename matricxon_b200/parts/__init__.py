@@ -1,7 +1,7 @@
 """Parts a model is assembled from. Importing this package registers the built-in kinds."""
 
 from matricxon_b200.parts import (  # noqa: F401  (registration)
-    attention, block, latent_attention, mlp, norm, recurrent, rotary)
+    attention, block, latent_attention, linear_attention, mlp, norm, recurrent, rotary, routed)
 from matricxon_b200.parts.base import (
     Block,
     CacheBinding,

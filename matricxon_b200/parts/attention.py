@@ -99,10 +99,14 @@ def simt_splits(ctx, n_heads: int, n_kv_heads: int, head_dim: int, window: int |
     return n_splits, ctx.scratch(kernels.attention_scratch_bytes(ctx.n_tokens, n_heads, head_dim, n_splits))
 
 
-def paged_attend(q, q_stride, ctx, binding, rt, n_heads, n_kv_heads, head_dim, window, scale):
+def paged_attend(q, q_stride, ctx, binding, rt, n_heads, n_kv_heads, head_dim, window, scale, softcap=None,
+                 sink=None):
     """Attention of the step's query rows (``q``: query head h of a row at column ``h * head_dim``, rows
     ``q_stride`` apart) over the keys and values already stored in ``binding.kv``: picks the kernel, the
-    tiles and the key splits for this step. Returns [tokens, heads * head_dim] in the runtime dtype."""
+    tiles and the key splits for this step. Returns [tokens, heads * head_dim] in the runtime dtype.
+    ``softcap`` caps the scaled scores at ``softcap * tanh(score / softcap)``; ``sink`` (float32, one logit per
+    head) joins the softmax's denominator without a value. Every kernel takes both."""
+    extras = {"softcap": softcap, "sink": sink}
     group = ctx.groups[binding.group]
     attn = torch.empty((ctx.n_tokens, n_heads * head_dim), dtype=rt.dtype, device=q.device)
     if kernels.mma_attention_supported(rt.dtype, head_dim, rt.page_size, q_stride):
@@ -121,7 +125,7 @@ def paged_attend(q, q_stride, ctx, binding, rt, n_heads, n_kv_heads, head_dim, w
                                            ctx.context_lens, tiles, n_tiles, ctx.n_tokens,
                                            n_heads, n_kv_heads, head_dim,
                                            window, scale, attn, ctx.status,
-                                           n_splits=n_splits, scratch=scratch)
+                                           n_splits=n_splits, scratch=scratch, **extras)
                 continue
             alone = (n_wide == 0) if is_narrow else (n_narrow == 0)
             if is_narrow and ctx.padded:
@@ -132,14 +136,14 @@ def paged_attend(q, q_stride, ctx, binding, rt, n_heads, n_kv_heads, head_dim, w
                                         ctx.cu_q, ctx.context_lens, tiles, n_tiles, is_narrow,
                                         ctx.n_tokens, n_heads, n_kv_heads,
                                         head_dim, window, scale, attn, ctx.status,
-                                        n_splits=n_splits, scratch=scratch)
+                                        n_splits=n_splits, scratch=scratch, **extras)
     else:
         n_splits, scratch = simt_splits(ctx, n_heads, n_kv_heads,
                                                  head_dim, window)
         kernels.paged_attention(q, q_stride, binding.kv, group.block_tables, ctx.tok_seq,
                                 ctx.positions, ctx.n_tokens, n_heads, n_kv_heads,
                                 head_dim, window, scale, attn, ctx.status,
-                                n_splits=n_splits, scratch=scratch)
+                                n_splits=n_splits, scratch=scratch, **extras)
     return attn
 
 
@@ -295,3 +299,115 @@ class GatedAttention(Mixer):
             return linear(attn, self.o_weight, None, EPILOGUE_F32, backend=rt.gemm_backend)
         return linear(attn, self.o_weight, None, EPILOGUE_RESIDUAL, residual=residual, out=residual,
                       backend=rt.gemm_backend)
+
+
+@register_part("mixer", "sink_attention")
+class SinkAttention(Mixer):
+    """Grouped-query attention with biased projections, a rotation of the first entries of every head, capped
+    scores, a sink logit per head in the softmax's denominator, values that may be blended with an earlier
+    layer's values of the same token, and one sigmoid gate per head (``SinkAttentionSpec``).
+
+    One fused product gives float rows ``[q | k | v | gate]`` with the biases added; one kernel rotates q and k in
+    float, blends the values and stores k and v in the paged cache in the layout the stock attention kernels
+    read (``paged_attend``, which caps the scores and counts the sink), every head padded with zeros to a common
+    size of a multiple of 16 when the key and value widths differ or are no such multiple; one kernel applies
+    the gate and drops the padding. A layer whose ``value_mix`` is ``"source"`` leaves its float values in the
+    step's memo under ``value_mix_key``; a ``"blend"`` layer reads them there."""
+
+    capturable = True
+
+    def __init__(self, spec, runtime, prefix):
+        super().__init__(spec, runtime, prefix)
+        self.padded_dim = self.cache_head_dim(spec)
+        self.position = (build_part("position", spec.position, runtime, prefix)
+                         if spec.position is not None else None)
+
+    @staticmethod
+    def cache_head_dim(spec) -> int:
+        return -(-max(spec.head_dim, spec.value_dim) // 16) * 16
+
+    @classmethod
+    def _matrices(cls, spec):
+        """(name, shape, has a bias) of the projections, in the order of the fused product's rows."""
+        shapes = [(spec.query_name, (spec.num_heads * spec.head_dim, spec.hidden_size), spec.bias),
+                  (spec.key_name, (spec.num_kv_heads * spec.head_dim, spec.hidden_size), spec.bias),
+                  (spec.value_name, (spec.num_kv_heads * spec.value_dim, spec.hidden_size), spec.bias)]
+        if spec.gate_name is not None:
+            shapes.append((spec.gate_name, (spec.num_heads, spec.hidden_size), False))
+        return shapes
+
+    @classmethod
+    def weight_specs(cls, spec, prefix):
+        specs = []
+        for name, shape, biased in cls._matrices(spec):
+            specs.append(WeightSpec(prefix + name, shape, role="matrix", init="weight"))
+            if biased:
+                specs.append(WeightSpec(prefix + name + spec.bias_suffix, (shape[0],), role="vector", init="bias"))
+        specs.append(WeightSpec(prefix + spec.output_name, (spec.hidden_size, spec.num_heads * spec.value_dim),
+                                role="matrix", init="weight"))
+        if spec.sink_name is not None:
+            specs.append(WeightSpec(prefix + spec.sink_name, (spec.num_heads,), role="vector", init="bias"))
+        if spec.value_mix_name is not None:
+            specs.append(WeightSpec(prefix + spec.value_mix_name, (), role="vector", init="bias"))
+        return specs
+
+    @classmethod
+    def cache_request(cls, spec):
+        return KVCacheRequest(num_kv_heads=spec.num_kv_heads, head_dim=cls.cache_head_dim(spec), window=spec.window)
+
+    def load(self, fetch):
+        p, s = self.prefix, self.spec
+        matrices = self._matrices(s)
+        self.proj_weight = torch.cat([fetch(p + name) for name, _, _ in matrices])
+        self.proj_bias = None
+        if s.bias:
+            self.proj_bias = torch.cat([fetch(p + name + s.bias_suffix) if biased else
+                                        torch.zeros(shape[0], dtype=torch.float32, device=self.runtime.device)
+                                        for name, shape, biased in matrices])
+        self.o_weight = fetch(p + s.output_name)
+        self.sink = fetch(p + s.sink_name) if s.sink_name is not None else None
+        # the scalar is read even where the layer does not blend (a source layer's is unused)
+        self.value_mix = fetch(p + s.value_mix_name).reshape(1) if s.value_mix_name is not None else None
+
+    def forward(self, h, residual, ctx, binding):
+        s, rt, hd = self.spec, self.runtime, self.padded_dim
+        if binding.kv is None:
+            raise RuntimeError("attention needs cache pages bound to it")
+        n = h.shape[0]
+        proj = linear(h, self.proj_weight, self.proj_bias, EPILOGUE_F32, backend=rt.gemm_backend)
+        v_col = (s.num_heads + s.num_kv_heads) * s.head_dim
+        v_width = s.num_kv_heads * s.value_dim
+        other = None
+        if s.value_mix is not None:
+            if s.value_mix == "blend":
+                other = ctx.memo.get(s.value_mix_key)
+                if other is None:
+                    raise RuntimeError("a layer blends values, but no earlier layer of this step published any")
+            else:
+                # every run of the step publishes anew: a captured run must not read what its warm-up run left
+                ctx.memo[s.value_mix_key] = proj[:, v_col:v_col + v_width]
+        if other is not None and other.shape[1] != v_width:
+            raise RuntimeError(f"cannot blend values of width {v_width} with published values of width {other.shape[1]}")
+        q = torch.empty((n, s.num_heads * hd), dtype=rt.dtype, device=h.device)
+        writes = binding.writes
+        if self.position is not None:
+            freq, rot = self.position.frequencies, s.position.rotary_dim
+        else:
+            freq, rot = torch.empty(0, dtype=torch.float32, device=h.device), 0
+        kernels.rotate_mix_kv_write(proj, ctx.positions, freq, rot, other, self.value_mix if other is not None else None,
+                                    ctx.groups[binding.group].slots if writes else None,
+                                    binding.kv if writes else None, q, s.num_heads, s.num_kv_heads, s.head_dim,
+                                    s.value_dim, ctx.status)
+        attn = paged_attend(q, q.stride(0), ctx, binding, rt, s.num_heads, s.num_kv_heads, hd, s.window, s.scale,
+                            softcap=s.softcap, sink=self.sink)
+        if s.gate_name is not None:
+            gate_col = v_col + v_width
+            gated = torch.empty((n, s.num_heads * s.value_dim), dtype=rt.dtype, device=h.device)
+            kernels.head_gate(attn, proj[:, gate_col:gate_col + s.num_heads], gated, s.num_heads, s.value_dim)
+            attn = gated
+        elif hd != s.value_dim:
+            attn = attn.view(n, s.num_heads, hd)[:, :, :s.value_dim].reshape(n, -1)
+        if residual is None:
+            return linear(attn, self.o_weight, None, EPILOGUE_F32, backend=rt.gemm_backend)
+        return linear(attn, self.o_weight, None, EPILOGUE_RESIDUAL, residual=residual, out=residual,
+                      backend=rt.gemm_backend, defer_sum=getattr(ctx, "sums_may_pend", False))

@@ -1,7 +1,7 @@
 """Arrangements of a mixer, a feed-forward and their norms inside one layer.
 
 ``pre_norm_sequential``: ``x = x + mixer(norm1(x)); x = x + ffn(norm2(x))``
-(app/architectures/starcoder2_layers.py:67-68). The residual stream ``x`` is float32
+(app/architectures/starcoder2_layers.py:67-68); a layer without a feed-forward has only the first sublayer. The residual stream ``x`` is float32
 and each sub-layer adds into it in float.
 """
 
@@ -19,27 +19,33 @@ class PreNormSequentialBlock(Block):
 
     def __init__(self, spec, runtime, prefix):
         super().__init__(spec, runtime, prefix)
-        self.mixer_norm = build_part("norm", spec.mixer_norm, runtime, f"{prefix}{spec.mixer_norm_name}.")
-        self.mixer = build_part("mixer", spec.mixer, runtime, f"{prefix}{spec.mixer_name}.")
-        self.ffn_norm = build_part("norm", spec.ffn_norm, runtime, f"{prefix}{spec.ffn_norm_name}.")
-        self.feed_forward = build_part("feed_forward", spec.feed_forward, runtime,
-                                       f"{prefix}{spec.feed_forward_name}.")
+        sep = spec.part_separator
+        self.mixer_norm = build_part("norm", spec.mixer_norm, runtime, f"{prefix}{spec.mixer_norm_name}{sep}")
+        self.mixer = build_part("mixer", spec.mixer, runtime, f"{prefix}{spec.mixer_name}{sep}")
+        # a layer may have only the mixer sublayer
+        self.ffn_norm = self.feed_forward = None
+        if spec.feed_forward is not None:
+            self.ffn_norm = build_part("norm", spec.ffn_norm, runtime, f"{prefix}{spec.ffn_norm_name}{sep}")
+            self.feed_forward = build_part("feed_forward", spec.feed_forward, runtime,
+                                           f"{prefix}{spec.feed_forward_name}{sep}")
         self.capturable = all(part.capturable for part in self.parts())
 
     @classmethod
     def weight_specs(cls, spec, prefix):
         from matricxon_b200.parts.base import part_class
 
+        groups = [("norm", spec.mixer_norm, spec.mixer_norm_name), ("mixer", spec.mixer, spec.mixer_name)]
+        if spec.feed_forward is not None:
+            groups += [("norm", spec.ffn_norm, spec.ffn_norm_name),
+                       ("feed_forward", spec.feed_forward, spec.feed_forward_name)]
         out = []
-        for category, sub, name in (("norm", spec.mixer_norm, spec.mixer_norm_name),
-                                    ("mixer", spec.mixer, spec.mixer_name),
-                                    ("norm", spec.ffn_norm, spec.ffn_norm_name),
-                                    ("feed_forward", spec.feed_forward, spec.feed_forward_name)):
-            out.extend(part_class(category, sub.kind).weight_specs(sub, f"{prefix}{name}."))
+        for category, sub, name in groups:
+            out.extend(part_class(category, sub.kind).weight_specs(sub, f"{prefix}{name}{spec.part_separator}"))
         return out
 
     def parts(self):
-        return (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)
+        return tuple(part for part in (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)
+                     if part is not None)
 
     def load(self, fetch):
         for part in self.parts():
@@ -63,8 +69,9 @@ class PreNormSequentialBlock(Block):
         try:
             x, h = self._normed(self.mixer_norm, x)
             x = self.mixer.forward(h, x, ctx, binding)
-            x, h = self._normed(self.ffn_norm, x)
-            x = self.feed_forward.forward(h, x, ctx)
+            if self.feed_forward is not None:
+                x, h = self._normed(self.ffn_norm, x)
+                x = self.feed_forward.forward(h, x, ctx)
         finally:
             ctx.sums_may_pend = False
         if isinstance(x, PendingSum) and not getattr(ctx, "pending_sum_wanted", False):

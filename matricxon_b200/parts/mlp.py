@@ -87,3 +87,49 @@ class ClampedGlu(FeedForward):
             return linear(mid, self.down_weight, None, EPILOGUE_F32, backend=backend)
         return linear(mid, self.down_weight, None, EPILOGUE_RESIDUAL, residual=residual, out=residual,
                       backend=backend)
+
+
+@register_part("feed_forward", "gated_mlp")
+class GatedMlp(FeedForward):
+    """``down(act(gate(h)) * up(h))`` without biases (``GatedMlpSpec``): one fused product for gate and up, one
+    activation kernel, the down product with the residual added. ``forward(h, None, ctx)`` returns the float
+    output without a residual."""
+
+    capturable = True
+
+    def __init__(self, spec, runtime, prefix):
+        super().__init__(spec, runtime, prefix)
+        from matricxon_b200.ops import kernels
+
+        if spec.activation not in kernels.GLU_ACTIVATIONS:
+            raise ValueError(f"feed-forward activation {spec.activation!r} has no kernel")
+
+    @classmethod
+    def weight_specs(cls, spec, prefix):
+        wide = (spec.intermediate_size, spec.hidden_size)
+        return [WeightSpec(prefix + spec.gate_name, wide, role="matrix", init="weight"),
+                WeightSpec(prefix + spec.up_name, wide, role="matrix", init="weight"),
+                WeightSpec(prefix + spec.down_name, (spec.hidden_size, spec.intermediate_size), role="matrix",
+                           init="weight")]
+
+    def load(self, fetch):
+        import torch
+
+        p, s = self.prefix, self.spec
+        self.gate_up_weight = torch.cat([fetch(p + s.gate_name), fetch(p + s.up_name)])
+        self.down_weight = fetch(p + s.down_name)
+
+    def forward(self, h, residual, ctx):
+        import torch
+
+        from matricxon_b200.ops import kernels
+        from matricxon_b200.ops.linear import EPILOGUE_F32, EPILOGUE_NONE
+
+        s, backend = self.spec, self.runtime.gemm_backend
+        gate_up = linear(h, self.gate_up_weight, None, EPILOGUE_NONE, backend=backend)
+        mid = torch.empty((h.shape[0], s.intermediate_size), dtype=gate_up.dtype, device=h.device)
+        kernels.glu(gate_up, mid, s.activation)
+        if residual is None:
+            return linear(mid, self.down_weight, None, EPILOGUE_F32, backend=backend)
+        return linear(mid, self.down_weight, None, EPILOGUE_RESIDUAL, residual=residual, out=residual,
+                      backend=backend, defer_sum=getattr(ctx, "sums_may_pend", False))

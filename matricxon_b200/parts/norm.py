@@ -82,3 +82,37 @@ class RmsNorm(Norm):
         act = torch.empty(tuple(x.shape), dtype=self.runtime.dtype, device=x.device)
         kernels.rmsnorm_sum(x, sublayer, skip_scale, self.weight, self.offset, self.spec.eps, act)
         return x, act
+
+
+@register_part("norm", "dynamic_tanh")
+class DynamicTanh(Norm):
+    """``tanh(alpha * x) * weight + shift`` on the float residual stream (``DynamicTanhSpec``): no mean, no
+    variance, one learned scalar. Float arithmetic, one rounding to the runtime dtype. Like LayerNorm it can form
+    a residual sum that a library product left unadded on its way through the rows."""
+
+    capturable = True
+    adds_pending_sum = True
+
+    @classmethod
+    def weight_specs(cls, spec, prefix):
+        return [WeightSpec(prefix + spec.weight_name, (spec.size,), role="vector", init="norm_weight"),
+                WeightSpec(prefix + spec.shift_name, (spec.size,), role="vector", init="norm_bias"),
+                WeightSpec(prefix + spec.alpha_name, (), role="vector", init="norm_weight")]
+
+    def load(self, fetch):
+        self.weight = fetch(self.prefix + self.spec.weight_name)
+        self.shift = fetch(self.prefix + self.spec.shift_name)
+        self.alpha = fetch(self.prefix + self.spec.alpha_name).reshape(1)
+
+    def forward(self, x, out=None, rows=None):
+        n_rows = x.shape[0] if rows is None else rows.numel()
+        if out is None:
+            out = torch.empty((n_rows, self.spec.size), dtype=self.runtime.dtype, device=x.device)
+        kernels.dyt(x, self.weight, self.shift, self.alpha, out, rows)
+        return out
+
+    def forward_sum(self, pending):
+        x = pending.added_by_kernel()
+        out = torch.empty(tuple(x.shape), dtype=self.runtime.dtype, device=x.device)
+        kernels.dyt(x, self.weight, self.shift, self.alpha, out, acc=pending.acc, col_bias=pending.bias)
+        return x, out

@@ -106,3 +106,39 @@ class InterpolatedRotary(PositionEncoding):
 
     def rotate_and_store(self, qkv, ctx, binding, n_heads, n_kv_heads, head_dim):
         raise NotImplementedError("an interpolated rotary table serves mixers that rotate in their own kernels")
+
+
+def wavelength_scaled_frequencies(spec) -> torch.Tensor:
+    """Radians per position of every pair of a ``WavelengthRotarySpec``, in float64 on the host: ``theta^(-2i/D)``,
+    kept for wavelengths below ``original / high``, divided by ``factor`` above ``original / low``, blended
+    linearly in ``original / wavelength`` between the two."""
+    import math
+
+    dims = spec.rotary_dim
+    out = []
+    for i in range(dims // 2):
+        f = spec.theta ** (-2.0 * i / dims)
+        if spec.factor is not None:
+            wavelength = 2.0 * math.pi / f
+            if wavelength > spec.original / spec.low:
+                f = f / spec.factor
+            elif wavelength >= spec.original / spec.high:
+                s = (spec.original / wavelength - spec.low) / (spec.high - spec.low)
+                f = (1.0 - s) * f / spec.factor + s * f
+        out.append(f)
+    return torch.tensor(out, dtype=torch.float64)
+
+
+@register_part("position", "rotary_wavelength")
+class WavelengthScaledRotary(PositionEncoding):
+    """Holds the frequency table (``frequencies``, float32 on the device) of a ``WavelengthRotarySpec`` for mixers
+    whose own kernels rotate a part of each head; angles are ``position * frequency`` in float there."""
+
+    capturable = True
+
+    def __init__(self, spec, runtime, prefix):
+        super().__init__(spec, runtime, prefix)
+        self.frequencies = wavelength_scaled_frequencies(spec).to(torch.float32).to(runtime.device)
+
+    def rotate_and_store(self, qkv, ctx, binding, n_heads, n_kv_heads, head_dim):
+        raise NotImplementedError("a wavelength-scaled table serves mixers that rotate in their own kernels")

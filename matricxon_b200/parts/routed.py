@@ -1,0 +1,75 @@
+"""A routed feed-forward: every token runs a few of many small gated feed-forwards.
+
+``RoutedExpertsSpec``: scores ``sigmoid(R h)`` in float, the experts in equal runs of neighbours, a run worth its
+two best scores, the best runs' experts eligible, the ``top`` best of them chosen; the output is
+``sum_e w_e down_e(act(gate_e h) * up_e h)`` with ``w = score / (sum of chosen scores + 1e-20) * route_scale``.
+
+The step never leaves the device and is stream-ordered: one kernel routes and counts every expert's (token, slot)
+pairs, two sort the pairs by expert and list the row tiles, two grouped products walk those tiles (the first gathers
+the tokens' rows and applies the gated activation, the second scales every pair's row by its weight), and one kernel
+adds a token's pairs to the residual stream in slot order, so that a token's result depends on nothing else in the
+batch. The experts' matrices are stacked at load: ``[experts, 2 ff, hidden]`` (gate rows, then up rows) and
+``[experts, hidden, ff]``. The router's matrix is held in float.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from matricxon_b200.ops import kernels
+from matricxon_b200.parts.base import FeedForward, register_part
+from matricxon_b200.weights.loader import WeightSpec
+
+
+@register_part("feed_forward", "routed_experts")
+class RoutedExperts(FeedForward):
+    capturable = True
+
+    def __init__(self, spec, runtime, prefix):
+        super().__init__(spec, runtime, prefix)
+        if spec.expert.activation not in kernels.GLU_ACTIVATIONS:
+            raise ValueError(f"expert activation {spec.expert.activation!r} has no kernel")
+
+    @classmethod
+    def weight_specs(cls, spec, prefix):
+        e = spec.expert
+        wide, narrow = (e.intermediate_size, spec.hidden_size), (spec.hidden_size, e.intermediate_size)
+        specs = []
+        for index in range(spec.num_experts):
+            q = prefix + spec.expert_format.format(index=index)
+            specs += [WeightSpec(q + e.gate_name, wide, role="matrix", init="weight"),
+                      WeightSpec(q + e.up_name, wide, role="matrix", init="weight"),
+                      WeightSpec(q + e.down_name, narrow, role="matrix", init="weight")]
+        # router logits are float: the matrix is held like a vector
+        specs.append(WeightSpec(prefix + spec.router_name, (spec.num_experts, spec.hidden_size), role="vector",
+                                init="weight"))
+        return specs
+
+    def load(self, fetch):
+        s, e = self.spec, self.spec.expert
+        names = [self.prefix + s.expert_format.format(index=index) for index in range(s.num_experts)]
+        self.gate_up = torch.stack([torch.cat([fetch(q + e.gate_name), fetch(q + e.up_name)]) for q in names])
+        self.down = torch.stack([fetch(q + e.down_name) for q in names])
+        self.router = fetch(self.prefix + s.router_name)
+
+    def forward(self, h, residual, ctx):
+        s, e = self.spec, self.spec.expert
+        n, device = h.shape[0], h.device
+        n_pairs = n * s.top
+        max_tiles = kernels.moe_max_tiles(n_pairs, s.num_experts)
+        # one int32 block for everything the routing leaves on the device
+        sizes = [s.num_experts, n_pairs, n_pairs, n_pairs, s.num_experts + 1, 3 * max_tiles, 1]
+        ints = torch.empty(sum(sizes), dtype=torch.int32, device=device)
+        counts, ids, place, order, first, tile_map, n_tiles = torch.split(ints, sizes)
+        counts.zero_()
+        weights = torch.empty(n_pairs, dtype=torch.float32, device=device)
+        kernels.moe_route(h, self.router, s.top, s.num_groups, s.groups_kept, s.route_scale, ids, weights, counts, place)
+        kernels.moe_plan(counts, ids, place, first, tile_map, n_tiles, order)
+        mid = torch.empty((n_pairs, e.intermediate_size), dtype=h.dtype, device=device)
+        kernels.moe_gemm(h, order, s.top, self.gate_up, tile_map, n_tiles, max_tiles, mid, None, e.activation)
+        pairs = torch.empty((n_pairs, s.hidden_size), dtype=torch.float32, device=device)
+        kernels.moe_gemm(mid, order, 1, self.down, tile_map, n_tiles, max_tiles, pairs, weights, None)
+        if residual is None:
+            residual = torch.zeros((n, s.hidden_size), dtype=torch.float32, device=device)
+        kernels.moe_combine(pairs, residual, s.top)
+        return residual

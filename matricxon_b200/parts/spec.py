@@ -239,6 +239,172 @@ class ClampedGluSpec:
 
 
 @dataclass(frozen=True)
+class DynamicTanhSpec:
+    """A norm without statistics: ``tanh(alpha * x) * weight + shift``, entry by entry, with one learned scalar
+    ``alpha``. The three tensors are ``<prefix><weight_name>``, ``<prefix><shift_name>`` and ``<prefix><alpha_name>``."""
+
+    size: int
+    weight_name: str = "weight"
+    shift_name: str = "bias"
+    alpha_name: str = "alpha"
+    kind: str = "dynamic_tanh"
+
+
+@dataclass(frozen=True)
+class WavelengthRotarySpec:
+    """Rotary encoding of the first ``rotary_dim`` entries of a head, halves paired as (i, i + rotary_dim/2), with
+    frequencies ``f_i = theta^(-2i/rotary_dim)`` rescaled by wavelength ``l = 2 pi / f`` for contexts longer than the
+    ``original`` one: kept where ``l < original / high``, divided by ``factor`` where ``l > original / low``, and
+    blended between, ``(1 - s) f / factor + s f`` with ``s = (original / l - low) / (high - low)``. ``factor`` None:
+    plain frequencies."""
+
+    rotary_dim: int
+    theta: float
+    factor: float | None = None
+    original: float = 0.0
+    low: float = 1.0
+    high: float = 4.0
+    kind: str = "rotary_wavelength"
+
+    def __post_init__(self) -> None:
+        if self.rotary_dim < 0 or self.rotary_dim % 2:
+            raise ValueError(f"a rotary encoding pairs dimensions: {self.rotary_dim} is odd or negative")
+        if self.factor is not None and not (self.factor > 0 and self.original > 0 and self.high > self.low > 0):
+            raise ValueError("wavelength scaling needs positive factor and original and 0 < low < high")
+
+
+@dataclass(frozen=True)
+class SinkAttentionSpec:
+    """Causal grouped-query attention with biased projections, a rotation of the first entries of every query and
+    key head (``position``; None: none), scores ``softcap * tanh(q . k * scale / softcap)`` (``softcap`` None: plain
+    scores), a learned logit per head that joins the softmax's denominator without a value (``sink_name`` None: no
+    sink), values of a width of their own, and one sigmoid gate per head on the output (``gate_name`` None: no gate).
+
+    ``value_mix`` ties layers together: a layer that says ``"source"`` publishes its values for the step's
+    tokens; a layer that says ``"blend"`` stores and attends over ``(1 - m) v + m v_source`` with its
+    learned scalar ``m`` (``value_mix_name``). Window rule as ``AttentionSpec``."""
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    window: int | None
+    scale: float
+    softcap: float | None
+    bias: bool
+    position: Any | None
+    query_name: str
+    key_name: str
+    value_name: str
+    output_name: str
+    gate_name: str | None = None
+    sink_name: str | None = None
+    value_mix: str | None = None              # None | "source" | "blend"
+    value_mix_name: str | None = None         # the scalar's tensor; declared for every layer that names it
+    value_mix_key: str = "value_mix"
+    bias_suffix: str = ".b"
+    kind: str = "sink_attention"
+
+    def __post_init__(self) -> None:
+        if self.num_kv_heads <= 0 or self.num_heads % self.num_kv_heads != 0:
+            raise ValueError(f"{self.num_heads} attention heads are no multiple of {self.num_kv_heads} kv heads")
+        if self.head_dim <= 0 or self.value_dim <= 0 or max(self.head_dim, self.value_dim) > 256:
+            raise ValueError(f"head sizes {self.head_dim} / {self.value_dim} are outside 1..256: "
+                             "no attention kernel of this engine takes them")
+        if self.value_mix not in (None, "source", "blend"):
+            raise ValueError(f"value_mix is None, 'source' or 'blend', not {self.value_mix!r}")
+        if self.value_mix == "blend" and self.value_mix_name is None:
+            raise ValueError("a layer that blends values needs the name of its mixing scalar")
+        if self.position is not None and self.position.rotary_dim > self.head_dim:
+            raise ValueError(f"{self.position.rotary_dim} rotated entries exceed the head of {self.head_dim}")
+        if self.softcap is not None and not self.softcap > 0:
+            raise ValueError(f"a score cap must be positive, got {self.softcap}")
+
+
+@dataclass(frozen=True)
+class GlaSpec:
+    """Gated linear attention: per head a state ``S <- diag(a_t) S + k_t v_t^T`` from S = 0 and ``o_t = S^T q_t``
+    with ``q = Wq h * query_scale``, ``k = Wk h`` (``head_dim`` wide), ``v = Wv h`` (``value_dim`` wide) and a decay
+    per key channel ``a = sigmoid(A2 (A1 h) + b)^(1/tau)``; every head's o is RMS-normalised over ``value_dim`` with
+    one plain weight shared by the heads, the heads are multiplied by ``silu(Wg h)`` and projected by Wo."""
+
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    value_dim: int
+    decay_rank: int
+    tau: float
+    query_scale: float
+    eps: float
+    query_name: str
+    key_name: str
+    value_name: str
+    gate_name: str
+    output_name: str
+    norm_name: str
+    decay_down_name: str                # A1 [rank, hidden]
+    decay_up_name: str                  # A2 [heads * head_dim, rank]
+    bias_suffix: str = ".b"
+    kind: str = "gla"
+
+    def __post_init__(self) -> None:
+        if min(self.num_heads, self.head_dim, self.value_dim, self.decay_rank) <= 0:
+            raise ValueError("gated linear attention needs positive head count, head sizes and decay rank")
+        if self.head_dim > 256:
+            raise ValueError(f"{self.head_dim} key channels per head: the recurrence kernel takes up to 256")
+        if not self.tau > 0:
+            raise ValueError(f"tau must be positive, got {self.tau}")
+
+
+@dataclass(frozen=True)
+class GatedMlpSpec:
+    """``down(act(gate(h)) * up(h))`` without biases; ``activation`` is ``gelu_tanh`` or ``silu``."""
+
+    hidden_size: int
+    intermediate_size: int
+    activation: str
+    gate_name: str
+    up_name: str
+    down_name: str
+    kind: str = "gated_mlp"
+
+
+@dataclass(frozen=True)
+class RoutedExpertsSpec:
+    """A mixture of ``num_experts`` gated feed-forwards (``GatedMlpSpec`` each, tensors under
+    ``<prefix><expert_format.format(index=e)>``), of which a token runs ``top``. Router logits ``R h`` and scores
+    ``sigmoid`` are float. The experts form ``num_groups`` equal runs of neighbours; a run is worth the sum of its
+    ``group_best`` largest scores and only the ``groups_kept`` best runs may supply experts. The output is the sum
+    of the chosen experts' outputs weighted by ``score / (sum of chosen scores + norm_eps) * route_scale``."""
+
+    hidden_size: int
+    num_experts: int
+    top: int
+    num_groups: int
+    groups_kept: int
+    route_scale: float
+    expert: Any                          # GatedMlpSpec
+    router_name: str
+    expert_format: str = "e{index}."
+    group_best: int = 2
+    norm_eps: float = 1e-20
+    kind: str = "routed_experts"
+
+    def __post_init__(self) -> None:
+        if not 0 < self.top <= self.num_experts:
+            raise ValueError(f"a token cannot run {self.top} of {self.num_experts} experts")
+        if self.num_groups <= 0 or self.num_experts % self.num_groups:
+            raise ValueError(f"{self.num_experts} experts cannot form {self.num_groups} equal groups")
+        if not 0 < self.groups_kept <= self.num_groups:
+            raise ValueError(f"{self.groups_kept} of {self.num_groups} groups cannot be kept")
+        if self.groups_kept * (self.num_experts // self.num_groups) < self.top:
+            raise ValueError(f"{self.groups_kept} kept groups hold fewer than {self.top} experts")
+        if self.group_best != 2 or self.norm_eps != 1e-20:
+            raise ValueError("the routing kernel ranks groups by their two best scores and adds 1e-20 to the sum")
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One decoder layer: which block arrangement holds which parts. ``feed_forward`` (with its norm)
     may be None for blocks that can do without; ``skip_scale`` is the weight of the skip path in blocks
@@ -255,6 +421,9 @@ class LayerSpec:
     ffn_norm_name: str
     block: str = "pre_norm_sequential"
     skip_scale: float = 1.0
+    # what the pre-norm block puts behind a part's name fragment to make its prefix ("" for checkpoints whose
+    # fragments carry their own separators, as the post-norm block expects them)
+    part_separator: str = "."
 
 
 @dataclass(frozen=True)
