@@ -15,6 +15,8 @@ time; ``points`` adds decoding at batch 1 and 64. Between timed iterations the w
 ``--compare busatar`` runs another workload instead and prints its own JSON line: the Busatar architecture
 beside StarCoder2 at equal width, heads, layers and feed-forward parameters (prefill of 2,048 tokens in one
 step and in 512-token steps, decode steps at several batch sizes; random weights of both).
+``--compare parunex`` does the same for the Parunex architecture beside Busatar, the closest of the engine's other
+models (mixed attention and recurrent layers, gated feed-forwards, a float residual stream).
 """
 
 from __future__ import annotations
@@ -356,6 +358,25 @@ def busatar_config(size: dict) -> dict:
             "norm": {"eps": 1e-5}, "layers": [pattern[i % 4] for i in range(COMPARE_LAYERS)]}
 
 
+def parunex_config(size: dict) -> dict:
+    """Attention and gated linear attention in turn, 128-wide heads on both sides, the first layer with a dense
+    gated feed-forward and the others with eight experts of half that width, two per token (the same active
+    feed-forward parameters as the dense one)."""
+    w, h = size["width"], size["width"] // 128
+    rot = {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 4096}}
+    dense = {"kind": "dense", "ff": size["ff"]}
+    routed = {"kind": "moe", "expert": {"ff": size["ff"] // 2},
+              "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 2}, "scale": 2.0}}
+    attention = {"type": "attention",
+                 "mixer": {"heads": h, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 50.0,
+                           "v_mix": True, "rot": rot}}
+    recurrence = {"type": "gla", "mixer": {"heads": h, "dim": 128, "vdim": 128, "tau": 16.0}}
+    layers = [dict(attention if i % 2 == 0 else recurrence, mlp=dense if i == 0 else routed)
+              for i in range(COMPARE_LAYERS)]
+    return {"architecture": "Parunex", "vocab": COMPARE_VOCAB, "width": w, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-5}, "layers": layers}
+
+
 def starcoder2_like(size: dict) -> dict:
     return dict(STARCODER2_3B, num_hidden_layers=COMPARE_LAYERS, hidden_size=size["width"],
                 num_attention_heads=size["width"] // 128, num_key_value_heads=4, head_dim=128,
@@ -453,15 +474,22 @@ def compare_designs(args) -> int:
     clocks.start()
     sizes = [s for s in args.compare_sizes.split(",") if s]
     batches = [int(b) for b in args.compare_batches.split(",")]
-    record = {"compare": "busatar vs starcoder2 at equal sizes", "layers": COMPARE_LAYERS, "vocab": COMPARE_VOCAB,
+    if args.compare == "parunex":
+        designs = (("parunex", parunex_config), ("busatar", busatar_config))
+    else:
+        designs = (("busatar", busatar_config), ("starcoder2", starcoder2_like))
+    record = {"compare": f"{designs[0][0]} vs {designs[1][0]} at equal sizes", "layers": COMPARE_LAYERS,
+              "vocab": COMPARE_VOCAB,
               "window": COMPARE_WINDOW, "context": args.context, "dtype": "bf16", "steps": args.steps,
               "warmup": max(args.warmup, 3), "peaks": peak_source, "hbm_gbs": peaks["hbm_gbs"],
               "data": "synthetic: seeded random weights, uniform random token ids", "sizes": {}}
     for name in sizes:
         size = COMPARE_SIZES[name]
         entry = {}
-        for design, raw in (("busatar", busatar_config(size)), ("starcoder2", starcoder2_like(size))):
-            entry[design] = measure_design(raw, args.context, batches, args.steps, max(args.warmup, 3),
+        for design, make in designs:
+            if args.compare_only and design != args.compare_only:
+                continue
+            entry[design] = measure_design(make(size), args.context, batches, args.steps, max(args.warmup, 3),
                                            use_graphs=not args.no_graphs)
         record["sizes"][name] = entry
     clocks.stop()
@@ -487,9 +515,11 @@ def main() -> int:
                         help="leave out the 7B and 15B workloads through the scheduler")
     parser.add_argument("--no-graphs", action="store_true",
                         help="launch every kernel of a decode step by itself (for profilers)")
-    parser.add_argument("--compare", choices=["busatar"], default=None,
-                        help="instead of the headline workload: Busatar beside StarCoder2 at equal layer sizes "
-                             "(prefill and decode throughput at a few sizes)")
+    parser.add_argument("--compare", choices=["busatar", "parunex"], default=None,
+                        help="instead of the headline workload: Busatar beside StarCoder2, or Parunex beside Busatar, "
+                             "at equal layer sizes (prefill and decode throughput at a few sizes)")
+    parser.add_argument("--compare-only", default=None,
+                        help="with --compare: measure only this one of the two designs (for profilers)")
     parser.add_argument("--compare-sizes", default="w1024,w2048")
     parser.add_argument("--compare-batches", default="1,8,32")
     args = parser.parse_args()

@@ -354,11 +354,20 @@ struct EpilogueLane {
 // in tensor memory (2 x 256 columns): the epilogue of one tile overlaps the products of the next.
 // `staged`: the epilogue goes through the 4 KB stages behind the operand stages (coalesced stores; needs
 // 16-byte-aligned rows, see mx_gemm_tcgen05); otherwise every lane stores its own row's pieces.
+// Grouped form (`groups.tile_map` set): the rows of A are sorted by group, every group has a weight matrix of its
+// own (N rows of the stacked W each), and the row tiles come from a list on the device: (group, first row, rows)
+// per tile, `n_row_tiles[0]` of them. A tile reads 128 rows of A from its first row on (the rows beyond its own
+// belong to the next group and are computed, but not stored) and the W rows `group * N + n0 ...`.
+struct TcGroups {
+    const int* tile_map;
+    const int* n_row_tiles;
+};
+
 template <bool F32>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    const float* __restrict__ bias, const float* residual, void* out, int ldo, int M,
-                    int N, int K, int bn, int mode, int staged, int kk, int* status) {
+                    const float* __restrict__ bias, const float* residual, void* out, int ldo, int M_all,
+                    int N, int K, int bn, int mode, int staged, int kk, int* status, const TcGroups groups) {
     const unsigned a_bytes = TC_BM * TC_BK * 2, w_bytes = (unsigned)bn * TC_BK * 2;
     // kk slices of K (64 wide each) share a stage and its barrier: with narrow tiles the fixed cost of a
     // stage (a barrier round trip in the producer and in the issuer) is what bounds the main loop
@@ -371,7 +380,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_slices = ((K + TC_BK - 1) / TC_BK + kk - 1) / kk;          // in stages
-    const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + bn - 1) / bn;
+    const bool grouped = groups.tile_map != nullptr;
+    const int tiles_m = grouped ? groups.n_row_tiles[0] : (M_all + TC_BM - 1) / TC_BM, tiles_n = (N + bn - 1) / bn;
     const int n_tiles = tiles_m * tiles_n;
 
     if (threadIdx.x == 0) {
@@ -403,7 +413,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int it = 0;
             bool alive = true;
             for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
-                const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * bn;
+                const int row_tile = tile % tiles_m;
+                const int m0 = grouped ? groups.tile_map[3 * row_tile + 1] : row_tile * TC_BM;
+                const int n0 = (tile / tiles_m) * bn + (grouped ? groups.tile_map[3 * row_tile] * N : 0);
                 for (int ks = 0; ks < k_slices; ++ks, ++it) {
                     const int s = it % TC_STAGES;
                     alive = tc_mbar_wait(&sh.empty[s], ((unsigned)(it / TC_STAGES) & 1) ^ 1, status);
@@ -458,7 +470,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         unsigned char* stage = tiles + (size_t)TC_STAGES * stage_bytes + (size_t)warp * 4096;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
             const int buf = local & 1;
-            const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * bn;
+            const int row_tile = tile % tiles_m;
+            const int m0 = grouped ? groups.tile_map[3 * row_tile + 1] : row_tile * TC_BM, n0 = (tile / tiles_m) * bn;
+            // a grouped tile ends where its group's rows end
+            const int M = grouped ? m0 + groups.tile_map[3 * row_tile + 2] : M_all;
             const unsigned tbase = tmem_base + (unsigned)buf * 256 + ((unsigned)(32 * warp) << 16);
             if (staged) {
                 EpilogueLane<F32> mine;
@@ -1129,9 +1144,65 @@ extern "C" int mx_gemm_tcgen05(const void* A, const void* W, const float* bias, 
     const int grid = (int)(tiles < n_sm ? tiles : n_sm);
     if (f32_out)
         gemm_tcgen05_kernel<true><<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, bias, residual, out, ldo, M, N, K,
-                                                                      bn, mode, vector_ok ? 1 : 0, kk, status);
+                                                                      bn, mode, vector_ok ? 1 : 0, kk, status,
+                                                                      TcGroups{nullptr, nullptr});
     else
         gemm_tcgen05_kernel<false><<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, bias, residual, out, ldo, M, N, K,
-                                                                       bn, mode, vector_ok ? 1 : 0, kk, status);
+                                                                       bn, mode, vector_ok ? 1 : 0, kk, status,
+                                                                       TcGroups{nullptr, nullptr});
+    return mx_launch_status();
+}
+
+// The grouped product on the 128-row kernel: A [rows, K] holds the rows of all groups, sorted by group; W
+// [groups * N, K] stacks the groups' matrices; `tile_map` ([tiles][3] = group, first row, rows; on the device, as
+// mx_moe_plan writes it for tiles of 128 rows) lists the row tiles and `n_row_tiles[0]` their number, which the
+// host only knows a bound of (`max_row_tiles`). out [rows, N]: bfloat16 (mode 0) or float (mode 3), no bias.
+extern "C" int mx_gemm_tcgen05_grouped(const void* A, const void* W, void* out, int out_dtype, int rows, int n_groups,
+                                       int N, int K, int lda, int ldw, int ldo, const int* tile_map,
+                                       const int* n_row_tiles, int max_row_tiles, int mode, int* status,
+                                       cudaStream_t stream) {
+    if (rows <= 0 || N <= 0 || max_row_tiles <= 0) return MX_OK;
+    if (K <= 0 || K % 8 != 0) MX_REFUSE("grouped tcgen05 gemm: K = %d is not a positive multiple of 8", K);
+    if (lda % 8 != 0 || ldw % 8 != 0)
+        MX_REFUSE("grouped tcgen05 gemm: row strides %d, %d are not multiples of 8 elements", lda, ldw);
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) % 16 != 0)
+        MX_REFUSE("grouped tcgen05 gemm: operands must start on 16-byte boundaries");
+    if (mode != 0 && mode != 3) MX_REFUSE("grouped tcgen05 gemm: epilogue mode %d (plain bfloat16 or float only)", mode);
+    if ((mode == 3) != (out_dtype == MX_DTYPE_F32))
+        MX_REFUSE("grouped tcgen05 gemm: epilogue mode %d does not write dtype %d", mode, out_dtype);
+    if (status == nullptr || tile_map == nullptr || n_row_tiles == nullptr)
+        MX_REFUSE("grouped tcgen05 gemm: needs a status word and the tile list");
+    if ((long long)n_groups * N > 0x7fffffffLL) MX_REFUSE("grouped tcgen05 gemm: too many stacked weight rows");
+    const int n_sm = sm_count();
+    const bool f32_out = mode == 3;
+    const bool vector_ok = (ldo * (f32_out ? 4 : 2)) % (f32_out ? 16 : 8) == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
+    static bool attribute_set = false;
+    if (!attribute_set) {
+        const size_t most = 226 * 1024;
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)most);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(gemm_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most);
+        if (e != cudaSuccess) MX_REFUSE("grouped tcgen05 gemm: cannot reserve %zu bytes of shared memory", most);
+        attribute_set = true;
+    }
+    // the width that suits `max_row_tiles` row tiles
+    const int bn = pick_tile_width(max_row_tiles * TC_BM, N, n_sm, TC_BM);
+    CUtensorMap map_a, map_w;
+    int rc = mx_tensor_map_2d(&map_a, A, rows, K, lda, TC_BM);
+    if (rc != MX_OK) return rc;
+    rc = mx_tensor_map_2d(&map_w, W, (long long)n_groups * N, K, ldw, bn);
+    if (rc != MX_OK) return rc;
+    int kk = 2 * TC_STAGES * (TC_BM + bn) * TC_BK * 2 + TC_STAGING + 1024 <= 226 * 1024 ? 2 : 1;
+    const size_t smem = (size_t)kk * TC_STAGES * (TC_BM + bn) * TC_BK * 2 + TC_STAGING + 1024;
+    const long long tiles = (long long)max_row_tiles * ((N + bn - 1) / bn);
+    const int grid = (int)(tiles < n_sm ? tiles : n_sm);
+    const TcGroups groups{tile_map, n_row_tiles};
+    if (f32_out)
+        gemm_tcgen05_kernel<true><<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, nullptr, nullptr, out, ldo, rows, N,
+                                                                      K, bn, mode, vector_ok ? 1 : 0, kk, status, groups);
+    else
+        gemm_tcgen05_kernel<false><<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, nullptr, nullptr, out, ldo, rows, N,
+                                                                       K, bn, mode, vector_ok ? 1 : 0, kk, status, groups);
     return mx_launch_status();
 }

@@ -16,6 +16,10 @@
 //   type. Plain form: rows are the sorted rows themselves, out[pair] = weight[pair] * product in float, one row per
 //   pair, so that the sum over a token's pairs can be formed in a fixed order.
 // mx_moe_combine: residual[t] += sum over the token's pairs, slot 0 first.
+// mx_moe_gather, mx_moe_combine_sorted: the ends of the tensor-core path. The grouped tcgen05 product
+//   (mx_gemm_tcgen05_grouped) reads its rows through TMA, so the tokens' rows are first copied into the order of
+//   the sorted pairs; it writes rows in that order too, and the combine step finds a pair's row at
+//   first[expert] + place and weighs it there. The plan's tiles are 128 rows then (32 for the FP32-core product).
 #include <math.h>
 
 #include "common.cuh"
@@ -110,7 +114,7 @@ moe_route_kernel(const T* __restrict__ h, int ld, const float* __restrict__ rout
         for (int slot = 32; slot < top; ++slot) weights[(size_t)t * top + slot] *= norm;
 }
 
-__global__ void moe_plan_kernel(const int* __restrict__ counts, int n_experts, int* __restrict__ first,
+__global__ void moe_plan_kernel(const int* __restrict__ counts, int n_experts, int tile_rows, int* __restrict__ first,
                                 int* __restrict__ tile_map, int* __restrict__ n_tiles) {
     extern __shared__ int plan_s[];               // [experts + 1]: first tile of every expert
     if (threadIdx.x == 0) {
@@ -119,7 +123,7 @@ __global__ void moe_plan_kernel(const int* __restrict__ counts, int n_experts, i
             first[e] = rows;
             plan_s[e] = tiles;
             rows += counts[e];
-            tiles += (counts[e] + MOE_BM - 1) / MOE_BM;
+            tiles += (counts[e] + tile_rows - 1) / tile_rows;
         }
         first[n_experts] = rows;
         plan_s[n_experts] = tiles;
@@ -128,10 +132,10 @@ __global__ void moe_plan_kernel(const int* __restrict__ counts, int n_experts, i
     __syncthreads();
     for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
         const int count = counts[e], row0 = first[e];
-        for (int i = 0, tile = plan_s[e]; i * MOE_BM < count; ++i, ++tile) {
+        for (int i = 0, tile = plan_s[e]; i * tile_rows < count; ++i, ++tile) {
             tile_map[3 * tile] = e;
-            tile_map[3 * tile + 1] = row0 + i * MOE_BM;
-            tile_map[3 * tile + 2] = min(MOE_BM, count - i * MOE_BM);
+            tile_map[3 * tile + 1] = row0 + i * tile_rows;
+            tile_map[3 * tile + 2] = min(tile_rows, count - i * tile_rows);
         }
     }
 }
@@ -228,6 +232,34 @@ __global__ void moe_combine_kernel(const float* __restrict__ pairs, float* __res
     residual[i] += sum;
 }
 
+// rows of the tokens' activations in the order of the sorted pairs: what a TMA-fed grouped product reads
+__global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ h, int ld, const int* __restrict__ order, int top,
+                                  __nv_bfloat16* __restrict__ sorted, int K8, long long count) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const long long r = i / K8;
+    const int c = (int)(i - r * K8);
+    const int token = order[r] / top;
+    reinterpret_cast<uint4*>(sorted)[i] = *reinterpret_cast<const uint4*>(h + (size_t)token * ld + 8 * c);
+}
+
+// residual[t] += sum over the token's pairs of weight[pair] * rows[place of the pair among the sorted rows]
+__global__ void moe_combine_sorted_kernel(const float* __restrict__ rows, const int* __restrict__ ids,
+                                          const int* __restrict__ place, const int* __restrict__ first,
+                                          const float* __restrict__ weight, float* __restrict__ residual, int top,
+                                          int width, long long count) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const long long t = i / width;
+    const int c = (int)(i - t * width);
+    float sum = 0.f;
+    for (int s = 0; s < top; ++s) {
+        const long long pair = t * top + s;
+        sum += weight[pair] * rows[((size_t)first[ids[pair]] + place[pair]) * width + c];
+    }
+    residual[i] += sum;
+}
+
 template <typename T>
 __global__ void glu_kernel(const T* __restrict__ gu, int ld, T* __restrict__ out, int ff, int act, long long count) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -263,11 +295,13 @@ extern "C" int mx_moe_route(const void* h, int dtype, int ld, const float* route
 
 extern "C" int mx_moe_tile_rows() { return MOE_BM; }
 
-extern "C" int mx_moe_plan(const int* counts, const int* ids, const int* place, int n_experts, int n_pairs, int* first,
-                           int* tile_map, int* n_tiles, int* order, cudaStream_t stream) {
+extern "C" int mx_moe_plan(const int* counts, const int* ids, const int* place, int n_experts, int n_pairs, int tile_rows,
+                           int* first, int* tile_map, int* n_tiles, int* order, cudaStream_t stream) {
     if (n_pairs <= 0) return MX_OK;
     if (n_experts > 8192) MX_REFUSE("routed feed-forward: %d experts", n_experts);
-    moe_plan_kernel<<<1, 256, (size_t)(n_experts + 1) * sizeof(int), stream>>>(counts, n_experts, first, tile_map, n_tiles);
+    if (tile_rows <= 0) MX_REFUSE("routed feed-forward: row tiles of %d rows", tile_rows);
+    moe_plan_kernel<<<1, 256, (size_t)(n_experts + 1) * sizeof(int), stream>>>(counts, n_experts, tile_rows, first,
+                                                                              tile_map, n_tiles);
     int rc = mx_launch_status();
     if (rc != MX_OK) return rc;
     moe_scatter_kernel<<<(n_pairs + 255) / 256, 256, 0, stream>>>(ids, place, first, order, n_pairs);
@@ -296,6 +330,27 @@ extern "C" int mx_moe_gemm(const void* a, int dtype, int lda, const int* order, 
         else MOE_LAUNCH(__nv_bfloat16, true, 1);
     }
 #undef MOE_LAUNCH
+    return mx_launch_status();
+}
+
+extern "C" int mx_moe_gather(const void* h, int ld, const int* order, int top, void* sorted, int n_pairs, int K,
+                             cudaStream_t stream) {
+    if (n_pairs <= 0) return MX_OK;
+    if (K % 8 != 0 || ld % 8 != 0 || ((uintptr_t)h | (uintptr_t)sorted) % 16 != 0)
+        MX_REFUSE("routed feed-forward: gathered rows must be 16-byte aligned (K = %d, stride %d)", K, ld);
+    const long long count = (long long)n_pairs * (K / 8);
+    moe_gather_kernel<<<(unsigned)((count + 255) / 256), 256, 0, stream>>>(
+        (const __nv_bfloat16*)h, ld, order, top, (__nv_bfloat16*)sorted, K / 8, count);
+    return mx_launch_status();
+}
+
+extern "C" int mx_moe_combine_sorted(const float* rows, const int* ids, const int* place, const int* first,
+                                     const float* weight, float* residual, int n_tokens, int top, int width,
+                                     cudaStream_t stream) {
+    const long long count = (long long)n_tokens * width;
+    if (count <= 0) return MX_OK;
+    moe_combine_sorted_kernel<<<(unsigned)((count + 255) / 256), 256, 0, stream>>>(rows, ids, place, first, weight,
+                                                                                   residual, top, width, count);
     return mx_launch_status();
 }
 

@@ -1033,24 +1033,25 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, top: int, n_groups: int, ke
 
 
 def moe_plan(counts: torch.Tensor, ids: torch.Tensor, place: torch.Tensor, first: torch.Tensor, tile_map: torch.Tensor,
-             n_tiles: torch.Tensor, order: torch.Tensor) -> None:
+             n_tiles: torch.Tensor, order: torch.Tensor, tile_rows: int | None = None) -> None:
     """From the routing's counts: ``first`` [experts + 1] (first sorted row of every expert), the row tiles
-    ``tile_map`` [tiles, 3] = (expert, first sorted row, rows) with their number in ``n_tiles`` [1], and
-    ``order`` [pairs]: the pairs sorted by expert."""
+    ``tile_map`` [tiles, 3] = (expert, first sorted row, rows) of at most ``tile_rows`` rows (default: the FP32-core
+    product's) with their number in ``n_tiles`` [1], and ``order`` [pairs]: the pairs sorted by expert."""
+    tile_rows = tile_rows or moe_tile_rows()
     for name, tensor in (("counts", counts), ("ids", ids), ("place", place), ("first", first), ("tile_map", tile_map),
                          ("n_tiles", n_tiles), ("order", order)):
         _need(tensor, name, torch.int32)
     n_experts, n_pairs = counts.numel(), ids.numel()
     assert first.numel() == n_experts + 1 and order.numel() == n_pairs
-    assert tile_map.numel() >= 3 * moe_max_tiles(n_pairs, n_experts)
-    check(library().mx_moe_plan(_ptr(counts), _ptr(ids), _ptr(place), n_experts, n_pairs, _ptr(first), _ptr(tile_map),
-                                _ptr(n_tiles), _ptr(order), _stream()), "moe_plan")
+    assert tile_map.numel() >= 3 * moe_max_tiles(n_pairs, n_experts, tile_rows)
+    check(library().mx_moe_plan(_ptr(counts), _ptr(ids), _ptr(place), n_experts, n_pairs, tile_rows, _ptr(first),
+                                _ptr(tile_map), _ptr(n_tiles), _ptr(order), _stream()), "moe_plan")
     _launched(2)
 
 
-def moe_max_tiles(n_pairs: int, n_experts: int) -> int:
+def moe_max_tiles(n_pairs: int, n_experts: int, tile_rows: int | None = None) -> int:
     """The most row tiles that ``n_pairs`` pairs shared out between ``n_experts`` experts can make."""
-    rows = moe_tile_rows()
+    rows = tile_rows or moe_tile_rows()
     return min(n_pairs, n_pairs // rows + n_experts)
 
 
@@ -1089,4 +1090,65 @@ def moe_combine(pairs: torch.Tensor, residual: torch.Tensor, top: int) -> None:
     n, width = residual.shape
     assert tuple(pairs.shape) == (n * top, width)
     check(library().mx_moe_combine(_ptr(pairs), _ptr(residual), n, top, width, _stream()), "moe_combine")
+    _launched()
+
+
+GROUPED_TILE_ROWS = 128      # row tiles of the grouped tcgen05 product
+
+
+def grouped_tcgen05_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether ``gemm_tcgen05_grouped`` takes rows ``a`` [rows, K] and stacked matrices ``w`` [groups, N, K]."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.stride(1) == 1
+            and a.stride(0) % 8 == 0 and w.is_contiguous() and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and w.shape[0] * w.shape[1] < 2 ** 31)
+
+
+def moe_gather(h: torch.Tensor, order: torch.Tensor, top: int, out: torch.Tensor) -> None:
+    """out[r] = h[order[r] // top]: the tokens' rows (bfloat16) in the order of the sorted pairs."""
+    _need(h, "h", torch.bfloat16, contiguous=False)
+    _need(order, "order", torch.int32)
+    _need(out, "out", torch.bfloat16)
+    n_pairs, k = out.shape
+    assert h.shape[1] == k and order.numel() == n_pairs and h.stride(1) == 1
+    check(library().mx_moe_gather(_ptr(h), h.stride(0), _ptr(order), top, _ptr(out), n_pairs, k, _stream()), "moe_gather")
+    _launched()
+
+
+def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, tile_map: torch.Tensor, n_tiles: torch.Tensor,
+                         max_tiles: int, out: torch.Tensor, status: torch.Tensor | None = None) -> None:
+    """out[r] = a[r] @ w[group of r].T on tcgen05: ``a`` [rows, K] bfloat16 sorted by group, ``w`` [groups, N, K],
+    ``tile_map`` / ``n_tiles`` from ``moe_plan(..., tile_rows=GROUPED_TILE_ROWS)``; ``out`` [rows, N] bfloat16 or
+    float32."""
+    _need(a, "a", torch.bfloat16, contiguous=False)
+    _need(w, "w", torch.bfloat16)
+    _need(out, "out")
+    _need(tile_map, "tile_map", torch.int32)
+    _need(n_tiles, "n_tiles", torch.int32)
+    rows, k = a.shape
+    groups, n = w.shape[0], w.shape[1]
+    assert w.shape[2] == k and tuple(out.shape) == (rows, n), (a.shape, w.shape, out.shape)
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelLibraryError(f"a grouped product writes bfloat16 or float32, not {out.dtype}")
+    if status is None:
+        status = default_status(a.device)
+    check(library().mx_gemm_tcgen05_grouped(_ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype), rows, groups, n, k,
+                                            a.stride(0), w.stride(1), out.stride(0), _ptr(tile_map), _ptr(n_tiles),
+                                            max_tiles, EPILOGUE_F32 if out.dtype == torch.float32 else EPILOGUE_NONE,
+                                            _ptr(status), _stream()), "gemm_tcgen05_grouped")
+    _launched()
+
+
+def moe_combine_sorted(rows: torch.Tensor, ids: torch.Tensor, place: torch.Tensor, first: torch.Tensor,
+                       weights: torch.Tensor, residual: torch.Tensor, top: int) -> None:
+    """residual[t] += sum over the token's ``top`` pairs of ``weights[pair] * rows[first[ids[pair]] + place[pair]]``
+    (``rows`` float32 [pairs, width] in sorted order), first slot first."""
+    _need(rows, "rows", torch.float32)
+    _need(residual, "residual", torch.float32)
+    _need(weights, "weights", torch.float32)
+    for name, tensor in (("ids", ids), ("place", place), ("first", first)):
+        _need(tensor, name, torch.int32)
+    n, width = residual.shape
+    assert tuple(rows.shape) == (n * top, width) and ids.numel() == n * top == place.numel() == weights.numel()
+    check(library().mx_moe_combine_sorted(_ptr(rows), _ptr(ids), _ptr(place), _ptr(first), _ptr(weights), _ptr(residual),
+                                          n, top, width, _stream()), "moe_combine_sorted")
     _launched()

@@ -66,7 +66,10 @@ _SIGNATURES: dict[str, tuple[list, object]] = {
     "mx_gla_norm_gate": ([P, P, I, P, F, P, I, I, I, I, P], I),
     "mx_moe_route": ([P, I, I, P, I, I, I, I, I, F, P, P, P, P, I, P], I),
     "mx_moe_tile_rows": ([], I),
-    "mx_moe_plan": ([P, P, P, I, I, P, P, P, P, P], I),
+    "mx_moe_plan": ([P, P, P, I, I, I, P, P, P, P, P], I),
+    "mx_moe_gather": ([P, I, P, I, P, I, I, P], I),
+    "mx_moe_combine_sorted": ([P, P, P, P, P, P, I, I, I, P], I),
+    "mx_gemm_tcgen05_grouped": ([P, P, P, I, I, I, I, I, I, I, I, P, P, I, I, P, P], I),
     "mx_moe_gemm": ([P, I, I, P, I, P, L, I, I, P, P, I, P, P, I, I, P], I),
     "mx_moe_combine": ([P, P, I, I, I, P], I),
     "mx_glu": ([P, I, P, I, I, I, I, P], I),

@@ -5,10 +5,12 @@ two best scores, the best runs' experts eligible, the ``top`` best of them chose
 ``sum_e w_e down_e(act(gate_e h) * up_e h)`` with ``w = score / (sum of chosen scores + 1e-20) * route_scale``.
 
 The step never leaves the device and is stream-ordered: one kernel routes and counts every expert's (token, slot)
-pairs, two sort the pairs by expert and list the row tiles, two grouped products walk those tiles (the first gathers
-the tokens' rows and applies the gated activation, the second scales every pair's row by its weight), and one kernel
-adds a token's pairs to the residual stream in slot order, so that a token's result depends on nothing else in the
-batch. The experts' matrices are stacked at load: ``[experts, 2 ff, hidden]`` (gate rows, then up rows) and
+pairs, two sort the pairs by expert and list the row tiles, two grouped products walk those tiles, and one kernel
+adds a token's weighted pairs to the residual stream in slot order, so that a token's result depends on nothing else
+in the batch. In bfloat16 the grouped products are the engine's tcgen05 product with a tile list (rows copied into
+sorted order first, the gated activation a kernel of its own, as in the dense feed-forward); in float32, and for sizes
+that TMA does not take, they run on the FP32 cores (the first gathers rows itself and applies the activation, the
+second weighs every pair's row). The experts' matrices are stacked at load: ``[experts, 2 ff, hidden]`` (gate rows, then up rows) and
 ``[experts, hidden, ff]``. The router's matrix is held in float.
 """
 
@@ -56,7 +58,11 @@ class RoutedExperts(FeedForward):
         s, e = self.spec, self.spec.expert
         n, device = h.shape[0], h.device
         n_pairs = n * s.top
-        max_tiles = kernels.moe_max_tiles(n_pairs, s.num_experts)
+        # bfloat16 with TMA-friendly sizes: the grouped products run on tcgen05 over rows copied into sorted order
+        on_tc = (self.runtime.gemm_backend == "auto" and kernels.grouped_tcgen05_supported(h, self.gate_up)
+                 and e.intermediate_size % 8 == 0 and s.hidden_size % 4 == 0)
+        tile_rows = kernels.GROUPED_TILE_ROWS if on_tc else kernels.moe_tile_rows()
+        max_tiles = kernels.moe_max_tiles(n_pairs, s.num_experts, tile_rows)
         # one int32 block for everything the routing leaves on the device
         sizes = [s.num_experts, n_pairs, n_pairs, n_pairs, s.num_experts + 1, 3 * max_tiles, 1]
         ints = torch.empty(sum(sizes), dtype=torch.int32, device=device)
@@ -64,12 +70,24 @@ class RoutedExperts(FeedForward):
         counts.zero_()
         weights = torch.empty(n_pairs, dtype=torch.float32, device=device)
         kernels.moe_route(h, self.router, s.top, s.num_groups, s.groups_kept, s.route_scale, ids, weights, counts, place)
-        kernels.moe_plan(counts, ids, place, first, tile_map, n_tiles, order)
+        kernels.moe_plan(counts, ids, place, first, tile_map, n_tiles, order, tile_rows)
+        if residual is None:
+            residual = torch.zeros((n, s.hidden_size), dtype=torch.float32, device=device)
+        if on_tc:
+            status = getattr(ctx, "status", None)
+            rows = torch.empty((n_pairs, s.hidden_size), dtype=h.dtype, device=device)
+            kernels.moe_gather(h, order, s.top, rows)
+            gate_up = torch.empty((n_pairs, 2 * e.intermediate_size), dtype=h.dtype, device=device)
+            kernels.gemm_tcgen05_grouped(rows, self.gate_up, tile_map, n_tiles, max_tiles, gate_up, status)
+            mid = torch.empty((n_pairs, e.intermediate_size), dtype=h.dtype, device=device)
+            kernels.glu(gate_up, mid, e.activation)
+            down = torch.empty((n_pairs, s.hidden_size), dtype=torch.float32, device=device)
+            kernels.gemm_tcgen05_grouped(mid, self.down, tile_map, n_tiles, max_tiles, down, status)
+            kernels.moe_combine_sorted(down, ids, place, first, weights, residual, s.top)
+            return residual
         mid = torch.empty((n_pairs, e.intermediate_size), dtype=h.dtype, device=device)
         kernels.moe_gemm(h, order, s.top, self.gate_up, tile_map, n_tiles, max_tiles, mid, None, e.activation)
         pairs = torch.empty((n_pairs, s.hidden_size), dtype=torch.float32, device=device)
         kernels.moe_gemm(mid, order, 1, self.down, tile_map, n_tiles, max_tiles, pairs, weights, None)
-        if residual is None:
-            residual = torch.zeros((n, s.hidden_size), dtype=torch.float32, device=device)
         kernels.moe_combine(pairs, residual, s.top)
         return residual
