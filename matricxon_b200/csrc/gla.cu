@@ -8,9 +8,10 @@
 //   every key channel, decay[t][c] = exp(log_sigmoid(A2[c] . low[t] + b[c]) / tau); A2 is float [channels][rank].
 //   The small second product stays on the FP32 cores so that no rounding enters the decay.
 // mx_gla_scan: every sequence's tokens in order, from and to the state slot [heads][dim][vdim] of the sequence.
-//   A block owns (sequence, head, 16 value columns); a thread owns one column and every eighth key channel of it,
-//   so the state stays in registers for the whole portion. Tokens arrive sixteen (eight for the widest heads) at a
-//   time through shared memory.
+//   A block owns (sequence, head, 16 value columns); a thread owns two columns and a sixteenth of their key
+//   channels (decay, key and query of a channel serve both columns), so the state stays in registers for the whole
+//   portion. Tokens arrive eight or sixteen at a time through shared memory; a thread's operands of the next token are in
+//   registers before it computes the current one, and the shares of an output are added up once a round.
 //   q is scaled by `q_scale` on its way in. Columns of a state are independent of one another, so cutting vdim
 //   into blocks changes no number.
 // mx_gla_norm_gate: out[t][h][e] = o[t][h][e] / sqrt(mean_e(o^2) + eps) * weight[e] * silu(gate[t][h][e]): the
@@ -22,81 +23,170 @@
 namespace {
 
 constexpr int GLA_COLS = 16;       // value columns per block
-constexpr int GLA_SLICES = 8;      // threads per column, each with every eighth key channel
-constexpr int GLA_THREADS = GLA_COLS * GLA_SLICES;
+constexpr int GLA_SLICES = 16;     // threads per pair of columns, each with a sixteenth of the key channels
+constexpr int GLA_THREADS = GLA_COLS / 2 * GLA_SLICES;
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 gla_decay_kernel(const float* __restrict__ low, int low_ld, const float* __restrict__ a2, const float* __restrict__ bias,
                  float inv_tau, float* __restrict__ decay, int channels, int rank) {
     extern __shared__ float low_s[];
-    const int t = blockIdx.x;
+    const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
     for (int r = threadIdx.x; r < rank; r += blockDim.x) low_s[r] = low[(size_t)t * low_ld + r];
     __syncthreads();
-    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
-        const float* w = a2 + (size_t)c * rank;
-        float z = bias ? bias[c] : 0.f;
+    if (c >= channels) return;
+    const float* w = a2 + (size_t)c * rank;
+    float z = bias ? bias[c] : 0.f;
+    if (rank % 4 == 0 && (reinterpret_cast<uintptr_t>(a2) & 15) == 0) {
+        // the row's loads set out together
+        for (int r = 0; r < rank; r += 16) {
+            float4 w4[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                w4[u] = (r + 4 * u < rank) ? *reinterpret_cast<const float4*>(w + r + 4 * u) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (r + 4 * u < rank) {
+                    z = fmaf(w4[u].x, low_s[r + 4 * u], z);
+                    z = fmaf(w4[u].y, low_s[r + 4 * u + 1], z);
+                    z = fmaf(w4[u].z, low_s[r + 4 * u + 2], z);
+                    z = fmaf(w4[u].w, low_s[r + 4 * u + 3], z);
+                }
+            }
+        }
+    } else {
         for (int r = 0; r < rank; ++r) z = fmaf(w[r], low_s[r], z);
-        // log(sigmoid(z)) without cancellation on either side
-        const float log_sig = z >= 0.f ? -log1pf(expf(-z)) : z - log1pf(expf(z));
-        decay[(size_t)t * channels + c] = expf(log_sig * inv_tau);
     }
+    // log(sigmoid(z)) without cancellation on either side
+    const float log_sig = z >= 0.f ? -log1pf(expf(-z)) : z - log1pf(expf(z));
+    decay[(size_t)t * channels + c] = expf(log_sig * inv_tau);
 }
 
-template <int ROWS, int GLA_TOKENS>     // key channels per thread: dim <= 8 * ROWS; tokens staged per round
+template <int ROWS, int GLA_TOKENS>     // key channels per thread: dim <= 16 * ROWS; tokens staged per round
 __global__ void __launch_bounds__(GLA_THREADS)
 gla_scan_kernel(const float* __restrict__ proj, int ld, int q_col, int k_col, int v_col, const float* __restrict__ decay,
                 float q_scale, float* __restrict__ state, const int* __restrict__ cu_q, const int* __restrict__ state_slots,
                 float* __restrict__ out, int n_heads, int dim, int vdim) {
-    __shared__ float q_s[GLA_TOKENS][8 * ROWS], k_s[GLA_TOKENS][8 * ROWS], a_s[GLA_TOKENS][8 * ROWS];
-    __shared__ float v_s[GLA_TOKENS][GLA_COLS];
+    // a thread's ROWS channels lie side by side, four floats of padding behind them: the 16-byte loads of the
+    // eight slices of a quarter warp then fall on different banks
+    constexpr int PAD = ROWS + 4, R4 = ROWS / 4, CH = GLA_SLICES * ROWS;
+    __shared__ __align__(16) float q_s[GLA_TOKENS][GLA_SLICES][PAD], k_s[GLA_TOKENS][GLA_SLICES][PAD],
+        a_s[GLA_TOKENS][GLA_SLICES][PAD];
+    __shared__ __align__(8) float v_s[GLA_TOKENS][GLA_COLS];
+    // a thread's share of every output of the round; the sixteen shares of an output are added up once a round
+    // (a shuffle chain per token would be the longest wait of the loop)
+    __shared__ __align__(8) float o_s[GLA_TOKENS][GLA_SLICES + 1][GLA_COLS];
     const int seq = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * GLA_COLS;
     const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
     if (t1 <= t0) return;
-    const int tid = threadIdx.x, slice = tid & (GLA_SLICES - 1), col = col0 + (tid >> 3);
-    const bool col_ok = col < vdim;
+    const int tid = threadIdx.x, slice = tid & (GLA_SLICES - 1), pair = tid / GLA_SLICES, col = col0 + 2 * pair;
     float* s_base = state + (((size_t)state_slots[seq] * n_heads + head) * dim) * vdim;
-    float S[ROWS];
+    float S0[ROWS], S1[ROWS];          // this thread's channels of columns col and col + 1
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
-        const int i = slice + GLA_SLICES * r;
-        S[r] = (col_ok && i < dim) ? s_base[(size_t)i * vdim + col] : 0.f;
+        const int i = slice * ROWS + r;
+        S0[r] = (col < vdim && i < dim) ? s_base[(size_t)i * vdim + col] : 0.f;
+        S1[r] = (col + 1 < vdim && i < dim) ? s_base[(size_t)i * vdim + col + 1] : 0.f;
     }
+    // A round's tokens travel global memory -> registers -> shared memory; the registers of the next round are
+    // asked for before this round is computed, so that the recurrence never waits for global memory.
+    constexpr int PER = GLA_TOKENS * CH / GLA_THREADS;             // (token, channel) items a thread stages per array
+    constexpr int V_PER = GLA_TOKENS * GLA_COLS / GLA_THREADS;
+    float q_r[PER], k_r[PER], a_r[PER], v_r[V_PER];
+    auto fetch = [&](int base) {
+        const int n_here = min(GLA_TOKENS, t1 - base);
+#pragma unroll
+        for (int u = 0; u < PER; ++u) {
+            const int item = tid + u * GLA_THREADS, j = item / CH, i = item % CH;
+            const bool live = j < n_here && i < dim;
+            const float* row = proj + (size_t)(base + j) * ld + head * dim + i;
+            q_r[u] = live ? row[q_col] : 0.f;
+            k_r[u] = live ? row[k_col] : 0.f;
+            a_r[u] = live ? decay[((size_t)(base + j) * n_heads + head) * dim + i] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < V_PER; ++u) {
+            const int item = tid + u * GLA_THREADS, j = item / GLA_COLS, c = item % GLA_COLS;
+            v_r[u] = (j < n_here && col0 + c < vdim) ? proj[(size_t)(base + j) * ld + v_col + head * vdim + col0 + c] : 0.f;
+        }
+    };
+    // one token's operands of this thread, from shared memory into registers (asked for one token ahead)
+    struct Operands {
+        float4 a[R4], k[R4], q[R4];
+        float2 v;
+    };
+    auto read = [&](Operands& into, int j) {
+#pragma unroll
+        for (int u = 0; u < R4; ++u) {
+            into.a[u] = *reinterpret_cast<const float4*>(&a_s[j][slice][4 * u]);
+            into.k[u] = *reinterpret_cast<const float4*>(&k_s[j][slice][4 * u]);
+            into.q[u] = *reinterpret_cast<const float4*>(&q_s[j][slice][4 * u]);
+        }
+        into.v = *reinterpret_cast<const float2*>(&v_s[j][2 * pair]);
+    };
+    auto advance = [&](const Operands& now, int j) {
+        float o0 = 0.f, o1 = 0.f, p0 = 0.f, p1 = 0.f;
+#pragma unroll
+        for (int u = 0; u < R4; ++u) {               // channels beyond dim hold zeros: no guard needed
+            const float av[4] = {now.a[u].x, now.a[u].y, now.a[u].z, now.a[u].w};
+            const float kv[4] = {now.k[u].x, now.k[u].y, now.k[u].z, now.k[u].w};
+            const float qv[4] = {now.q[u].x, now.q[u].y, now.q[u].z, now.q[u].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                S0[4 * u + e] = fmaf(av[e], S0[4 * u + e], kv[e] * now.v.x);
+                S1[4 * u + e] = fmaf(av[e], S1[4 * u + e], kv[e] * now.v.y);
+                if (e & 1) {
+                    o1 = fmaf(S0[4 * u + e], qv[e], o1);
+                    p1 = fmaf(S1[4 * u + e], qv[e], p1);
+                } else {
+                    o0 = fmaf(S0[4 * u + e], qv[e], o0);
+                    p0 = fmaf(S1[4 * u + e], qv[e], p0);
+                }
+            }
+        }
+        *reinterpret_cast<float2*>(&o_s[j][slice][2 * pair]) = make_float2(o0 + o1, p0 + p1);
+    };
+    fetch(t0);
     for (int base = t0; base < t1; base += GLA_TOKENS) {
         const int n_here = min(GLA_TOKENS, t1 - base);
         __syncthreads();
-        for (int item = tid; item < n_here * dim; item += GLA_THREADS) {
-            const int j = item / dim, i = item - j * dim;
-            const float* row = proj + (size_t)(base + j) * ld;
-            q_s[j][i] = row[q_col + head * dim + i] * q_scale;
-            k_s[j][i] = row[k_col + head * dim + i];
-            a_s[j][i] = decay[((size_t)(base + j) * n_heads + head) * dim + i];
+#pragma unroll
+        for (int u = 0; u < PER; ++u) {
+            const int item = tid + u * GLA_THREADS, j = item / CH, i = item % CH;
+            q_s[j][i / ROWS][i % ROWS] = q_r[u] * q_scale;
+            k_s[j][i / ROWS][i % ROWS] = k_r[u];
+            a_s[j][i / ROWS][i % ROWS] = a_r[u];
         }
-        for (int item = tid; item < n_here * GLA_COLS; item += GLA_THREADS) {
-            const int j = item / GLA_COLS, c = item - j * GLA_COLS;
-            v_s[j][c] = (col0 + c < vdim) ? proj[(size_t)(base + j) * ld + v_col + head * vdim + col0 + c] : 0.f;
+#pragma unroll
+        for (int u = 0; u < V_PER; ++u) {
+            const int item = tid + u * GLA_THREADS;
+            v_s[item / GLA_COLS][item % GLA_COLS] = v_r[u];
         }
         __syncthreads();
-        for (int j = 0; j < n_here; ++j) {
-            const float v = v_s[j][tid >> 3];
+        if (base + GLA_TOKENS < t1) fetch(base + GLA_TOKENS);
+        Operands even, odd;
+        read(even, 0);
+        for (int j = 0; j < n_here; j += 2) {
+            if (j + 1 < n_here) read(odd, j + 1);
+            advance(even, j);
+            if (j + 1 < n_here) {
+                if (j + 2 < n_here) read(even, j + 2);
+                advance(odd, j + 1);
+            }
+        }
+        __syncthreads();
+        for (int item = tid; item < n_here * GLA_COLS; item += GLA_THREADS) {
+            const int j = item / GLA_COLS, c = item % GLA_COLS;
             float o = 0.f;
 #pragma unroll
-            for (int r = 0; r < ROWS; ++r) {
-                const int i = slice + GLA_SLICES * r;
-                if (i < dim) {
-                    S[r] = fmaf(a_s[j][i], S[r], k_s[j][i] * v);
-                    o = fmaf(S[r], q_s[j][i], o);
-                }
-            }
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            o += __shfl_xor_sync(0xffffffffu, o, 4);
-            if (slice == 0 && col_ok) out[((size_t)(base + j) * n_heads + head) * vdim + col] = o;
+            for (int sl = 0; sl < GLA_SLICES; ++sl) o += o_s[j][sl][c];
+            if (col0 + c < vdim) out[((size_t)(base + j) * n_heads + head) * vdim + col0 + c] = o;
         }
     }
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
-        const int i = slice + GLA_SLICES * r;
-        if (col_ok && i < dim) s_base[(size_t)i * vdim + col] = S[r];
+        const int i = slice * ROWS + r;
+        if (col < vdim && i < dim) s_base[(size_t)i * vdim + col] = S0[r];
+        if (col + 1 < vdim && i < dim) s_base[(size_t)i * vdim + col + 1] = S1[r];
     }
 }
 
@@ -104,17 +194,33 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 gla_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ gate, int gate_ld,
                      const float* __restrict__ weight, float eps, T* __restrict__ out, int n_heads, int vdim) {
-    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
-    for (int h = warp; h < n_heads; h += n_warps) {
-        const float* src = o + ((size_t)t * n_heads + h) * vdim;
-        float s = 0.f;
-        for (int e = lane; e < vdim; e += 32) s = fmaf(src[e], src[e], s);
-        const float inv = 1.0f / sqrtf(warp_sum(s) / (float)vdim + eps);
-        for (int e = lane; e < vdim; e += 32) {
-            const float g = gate[(size_t)t * gate_ld + h * vdim + e];
-            const float silu = g / (1.0f + expf(-g));
-            out[((size_t)t * n_heads + h) * vdim + e] = from_float<T>(src[e] * inv * weight[e] * silu);
-        }
+    const int t = blockIdx.x, lane = threadIdx.x & 31;
+    const int h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (h >= n_heads) return;
+    const float* src = o + ((size_t)t * n_heads + h) * vdim;
+    const float* g_row = gate + (size_t)t * gate_ld + h * vdim;
+    constexpr int KEPT = 8;                       // up to 256 values of a head stay in registers
+    float val[KEPT], g[KEPT];
+    float s = 0.f;
+#pragma unroll
+    for (int u = 0; u < KEPT; ++u) {
+        const int e = lane + 32 * u;
+        val[u] = e < vdim ? src[e] : 0.f;
+        g[u] = e < vdim ? g_row[e] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < KEPT; ++u) s = fmaf(val[u], val[u], s);
+    for (int e = lane + 32 * KEPT; e < vdim; e += 32) s = fmaf(src[e], src[e], s);
+    const float inv = 1.0f / sqrtf(warp_sum(s) / (float)vdim + eps);
+#pragma unroll
+    for (int u = 0; u < KEPT; ++u) {
+        const int e = lane + 32 * u;
+        if (e < vdim)
+            out[((size_t)t * n_heads + h) * vdim + e] = from_float<T>(val[u] * inv * weight[e] * (g[u] / (1.0f + expf(-g[u]))));
+    }
+    for (int e = lane + 32 * KEPT; e < vdim; e += 32) {
+        const float gv = g_row[e];
+        out[((size_t)t * n_heads + h) * vdim + e] = from_float<T>(src[e] * inv * weight[e] * (gv / (1.0f + expf(-gv))));
     }
 }
 
@@ -125,8 +231,8 @@ extern "C" int mx_gla_decay(const float* low, int low_ld, const float* a2, const
     if (n_tokens <= 0) return MX_OK;
     if (!(tau > 0.f)) MX_REFUSE("gated linear attention: tau %f is not positive", tau);
     if (rank <= 0 || rank > 8192) MX_REFUSE("gated linear attention: a decay rank of %d", rank);
-    gla_decay_kernel<<<n_tokens, 128, (size_t)rank * sizeof(float), stream>>>(low, low_ld, a2, bias, 1.0f / tau, decay,
-                                                                             channels, rank);
+    gla_decay_kernel<<<dim3(n_tokens, (channels + 255) / 256), 256, (size_t)rank * sizeof(float), stream>>>(
+        low, low_ld, a2, bias, 1.0f / tau, decay, channels, rank);
     return mx_launch_status();
 }
 
@@ -135,16 +241,16 @@ extern "C" int mx_gla_scan(const float* proj, int ld, int q_col, int k_col, int 
                            int dim, int vdim, cudaStream_t stream) {
     if (n_seqs <= 0) return MX_OK;
     if (dim <= 0 || dim > 256) MX_REFUSE("gated linear attention: %d key channels per head (1..256)", dim);
-    if (n_heads > 65535) MX_REFUSE("gated linear attention: %d heads exceed the grid", n_heads);
+    if (n_heads > 65535 || vdim > 65535 * GLA_COLS) MX_REFUSE("gated linear attention: %d heads of %d values exceed the grid", n_heads, vdim);
     const dim3 grid(n_seqs, n_heads, (vdim + GLA_COLS - 1) / GLA_COLS);
     if (dim <= 64)
-        gla_scan_kernel<8, 16><<<grid, GLA_THREADS, 0, stream>>>(proj, ld, q_col, k_col, v_col, decay, q_scale, state, cu_q,
+        gla_scan_kernel<4, 16><<<grid, GLA_THREADS, 0, stream>>>(proj, ld, q_col, k_col, v_col, decay, q_scale, state, cu_q,
                                                             state_slots, out, n_heads, dim, vdim);
     else if (dim <= 128)
-        gla_scan_kernel<16, 16><<<grid, GLA_THREADS, 0, stream>>>(proj, ld, q_col, k_col, v_col, decay, q_scale, state, cu_q,
+        gla_scan_kernel<8, 8><<<grid, GLA_THREADS, 0, stream>>>(proj, ld, q_col, k_col, v_col, decay, q_scale, state, cu_q,
                                                              state_slots, out, n_heads, dim, vdim);
     else
-        gla_scan_kernel<32, 8><<<grid, GLA_THREADS, 0, stream>>>(proj, ld, q_col, k_col, v_col, decay, q_scale, state, cu_q,
+        gla_scan_kernel<16, 8><<<grid, GLA_THREADS, 0, stream>>>(proj, ld, q_col, k_col, v_col, decay, q_scale, state, cu_q,
                                                              state_slots, out, n_heads, dim, vdim);
     return mx_launch_status();
 }
@@ -153,9 +259,10 @@ extern "C" int mx_gla_norm_gate(const float* o, const float* gate, int gate_ld, 
                                 int dtype, int n_tokens, int n_heads, int vdim, cudaStream_t stream) {
     if (n_tokens <= 0) return MX_OK;
     if (dtype == MX_DTYPE_F32)
-        gla_norm_gate_kernel<float><<<n_tokens, 128, 0, stream>>>(o, gate, gate_ld, weight, eps, (float*)out, n_heads, vdim);
+        gla_norm_gate_kernel<float><<<dim3(n_tokens, (n_heads + 3) / 4), 128, 0, stream>>>(o, gate, gate_ld, weight, eps,
+                                                                                          (float*)out, n_heads, vdim);
     else
-        gla_norm_gate_kernel<__nv_bfloat16><<<n_tokens, 128, 0, stream>>>(o, gate, gate_ld, weight, eps,
-                                                                         (__nv_bfloat16*)out, n_heads, vdim);
+        gla_norm_gate_kernel<__nv_bfloat16><<<dim3(n_tokens, (n_heads + 3) / 4), 128, 0, stream>>>(
+            o, gate, gate_ld, weight, eps, (__nv_bfloat16*)out, n_heads, vdim);
     return mx_launch_status();
 }

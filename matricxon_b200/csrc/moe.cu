@@ -38,11 +38,11 @@ __device__ __forceinline__ void arg_best(float& v, int& i) {
 }
 
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 moe_route_kernel(const T* __restrict__ h, int ld, const float* __restrict__ router, int K, int n_experts, int top,
                  int n_groups, int keep, float scale, int* __restrict__ ids, float* __restrict__ weights,
                  int* __restrict__ counts, int* __restrict__ place) {
-    extern __shared__ float route_s[];
+    extern __shared__ __align__(16) float route_s[];
     float* h_s = route_s;                         // [K]
     float* score = h_s + K;                       // [experts]
     float* open = score + n_experts;              // [experts]: the score while the expert may still be chosen, else -1
@@ -50,10 +50,36 @@ moe_route_kernel(const T* __restrict__ h, int ld, const float* __restrict__ rout
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     for (int k = tid; k < K; k += blockDim.x) h_s[k] = to_float(h[(size_t)t * ld + k]);
     __syncthreads();
+    const bool vec = K % 4 == 0 && (reinterpret_cast<uintptr_t>(router) & 15) == 0;
     for (int e = warp; e < n_experts; e += blockDim.x >> 5) {
         const float* w = router + (size_t)e * K;
         float z = 0.f;
-        for (int k = lane; k < K; k += 32) z = fmaf(w[k], h_s[k], z);
+        if (vec) {
+            // four 16-byte loads of a lane set out together: a row of 2,048 costs four trips to memory, not 64
+            const float4* w4 = reinterpret_cast<const float4*>(w);
+            const float4* h4 = reinterpret_cast<const float4*>(h_s);
+            const int k4 = K >> 2;
+            float zz[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int k = lane; k < k4; k += 128) {
+                float4 wv[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    wv[u] = (k + 32 * u < k4) ? w4[k + 32 * u] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (k + 32 * u < k4) {
+                        const float4 hv = h4[k + 32 * u];
+                        zz[u] = fmaf(wv[u].x, hv.x, zz[u]);
+                        zz[u] = fmaf(wv[u].y, hv.y, zz[u]);
+                        zz[u] = fmaf(wv[u].z, hv.z, zz[u]);
+                        zz[u] = fmaf(wv[u].w, hv.w, zz[u]);
+                    }
+                }
+            }
+            z = (zz[0] + zz[1]) + (zz[2] + zz[3]);
+        } else {
+            for (int k = lane; k < K; k += 32) z = fmaf(w[k], h_s[k], z);
+        }
         z = warp_sum(z);
         if (lane == 0) score[e] = 1.0f / (1.0f + expf(-z));
     }
@@ -271,6 +297,29 @@ __global__ void glu_kernel(const T* __restrict__ gu, int ld, T* __restrict__ out
     out[i] = from_float<T>((act == 0 ? gelu_tanh(g) : act_silu(g)) * u);
 }
 
+// eight neighbouring columns a thread, 16-byte accesses (bfloat16 rows whose width and stride are multiples of 8)
+__global__ void glu_vec_kernel(const __nv_bfloat16* __restrict__ gu, int ld, __nv_bfloat16* __restrict__ out, int ff,
+                               int act, long long groups) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= groups) return;
+    const int per_row = ff >> 3;
+    const long long t = i / per_row;
+    const int c = (int)(i - t * per_row) << 3;
+    const uint4 graw = *reinterpret_cast<const uint4*>(gu + (size_t)t * ld + c);
+    const uint4 uraw = *reinterpret_cast<const uint4*>(gu + (size_t)t * ld + ff + c);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&graw);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uraw);
+    uint4 oraw;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&oraw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float g0 = __low2float(g2[e]), g1 = __high2float(g2[e]);
+        const float a0 = act == 0 ? gelu_tanh(g0) : act_silu(g0), a1 = act == 0 ? gelu_tanh(g1) : act_silu(g1);
+        o2[e] = __floats2bfloat162_rn(a0 * __low2float(u2[e]), a1 * __high2float(u2[e]));
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)t * ff + c) = oraw;
+}
+
 }  // namespace
 
 extern "C" int mx_moe_route(const void* h, int dtype, int ld, const float* router, int K, int n_experts, int top,
@@ -284,10 +333,10 @@ extern "C" int mx_moe_route(const void* h, int dtype, int ld, const float* route
     const size_t smem = ((size_t)K + 2 * (size_t)n_experts + n_groups) * sizeof(float);
     if (smem > 48 * 1024) MX_REFUSE("router: %zu bytes of shared memory for K = %d and %d experts", smem, K, n_experts);
     if (dtype == MX_DTYPE_F32)
-        moe_route_kernel<float><<<n_tokens, 128, smem, stream>>>((const float*)h, ld, router, K, n_experts, top, n_groups,
+        moe_route_kernel<float><<<n_tokens, 256, smem, stream>>>((const float*)h, ld, router, K, n_experts, top, n_groups,
                                                                 keep, scale, ids, weights, counts, place);
     else
-        moe_route_kernel<__nv_bfloat16><<<n_tokens, 128, smem, stream>>>((const __nv_bfloat16*)h, ld, router, K, n_experts,
+        moe_route_kernel<__nv_bfloat16><<<n_tokens, 256, smem, stream>>>((const __nv_bfloat16*)h, ld, router, K, n_experts,
                                                                         top, n_groups, keep, scale, ids, weights, counts,
                                                                         place);
     return mx_launch_status();
@@ -366,6 +415,12 @@ extern "C" int mx_glu(const void* gu, int ld, void* out, int dtype, int n_tokens
     const long long count = (long long)n_tokens * ff;
     if (count <= 0) return MX_OK;
     const unsigned blocks = (unsigned)((count + 255) / 256);
+    if (dtype == MX_DTYPE_BF16 && ff % 8 == 0 && ld % 8 == 0 && ((uintptr_t)gu | (uintptr_t)out) % 16 == 0) {
+        const long long groups = count >> 3;
+        glu_vec_kernel<<<(unsigned)((groups + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)gu, ld,
+                                                                             (__nv_bfloat16*)out, ff, act, groups);
+        return mx_launch_status();
+    }
     if (dtype == MX_DTYPE_F32)
         glu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, ld, (float*)out, ff, act, count);
     else

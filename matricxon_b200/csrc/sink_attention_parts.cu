@@ -39,7 +39,10 @@ rotate_mix_kv_write_kernel(const float* __restrict__ proj, int ld, const int* __
     T* kbase = cache + ((size_t)page * 2 * n_kv_heads) * head_stride + (size_t)offset * hd;
     T* vbase = cache + ((size_t)page * 2 * n_kv_heads + n_kv_heads) * head_stride + offset;
     const int rot_heads = n_heads + (slot >= 0 ? n_kv_heads : 0);
-    for (int item = threadIdx.x; item < rot_heads * hd; item += blockDim.x) {
+    // blockIdx.y shares a token's items out between blocks: the few tokens of a decode step then cost one trip
+    // to memory instead of one per 128 items
+    const int stride = blockDim.x * gridDim.y, start = blockIdx.y * blockDim.x + threadIdx.x;
+    for (int item = start; item < rot_heads * hd; item += stride) {
         const int h = item / hd, d = item - h * hd;
         const float* src = row + (size_t)h * dim;            // k heads follow the q heads directly
         float value = 0.f;
@@ -57,7 +60,7 @@ rotate_mix_kv_write_kernel(const float* __restrict__ proj, int ld, const int* __
     if (slot < 0) return;
     const float* vrow = row + (size_t)(n_heads + n_kv_heads) * dim;
     const float mix = (other && mix_ptr) ? mix_ptr[0] : 0.f;
-    for (int item = threadIdx.x; item < n_kv_heads * hd; item += blockDim.x) {
+    for (int item = start; item < n_kv_heads * hd; item += stride) {
         const int h = item / hd, d = item - h * hd;
         float value = 0.f;
         if (d < vdim) {
@@ -95,12 +98,15 @@ extern "C" int mx_rotate_mix_kv_write(const float* proj, int ld, const int* posi
     if (rot < 0 || rot % 2 != 0 || rot > dim) MX_REFUSE("attention operands: %d rotated entries in a head of %d", rot, dim);
     if (ld < (n_heads + n_kv_heads) * dim + n_kv_heads * vdim) MX_REFUSE("attention operands: projection rows are too short");
     const long long n_slots = n_pages * page_size;
+    // few tokens: as many blocks per token as the items allow; many tokens fill the GPU by themselves
+    const int pieces = n_tokens >= 512 ? 1 : max(1, min(32, ((n_heads + n_kv_heads) * hd + 127) / 128));
+    const dim3 grid(n_tokens, pieces);
     if (dtype == MX_DTYPE_F32)
-        rotate_mix_kv_write_kernel<float><<<n_tokens, 128, 0, stream>>>(
+        rotate_mix_kv_write_kernel<float><<<grid, 128, 0, stream>>>(
             proj, ld, positions, freq, rot, other, other_ld, mix, cache ? slots : nullptr, (float*)cache, n_slots,
             page_size, (float*)q_out, n_heads, n_kv_heads, dim, vdim, hd, status);
     else
-        rotate_mix_kv_write_kernel<__nv_bfloat16><<<n_tokens, 128, 0, stream>>>(
+        rotate_mix_kv_write_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(
             proj, ld, positions, freq, rot, other, other_ld, mix, cache ? slots : nullptr, (__nv_bfloat16*)cache, n_slots,
             page_size, (__nv_bfloat16*)q_out, n_heads, n_kv_heads, dim, vdim, hd, status);
     return mx_launch_status();
