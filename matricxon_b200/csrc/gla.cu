@@ -74,7 +74,7 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_col, int k_col, in
     __shared__ __align__(8) float v_s[GLA_TOKENS][GLA_COLS];
     // a thread's share of every output of the round; the sixteen shares of an output are added up once a round
     // (a shuffle chain per token would be the longest wait of the loop)
-    __shared__ __align__(8) float o_s[GLA_TOKENS][GLA_SLICES + 1][GLA_COLS];
+    __shared__ __align__(8) float o_s[GLA_TOKENS][GLA_SLICES][GLA_COLS + 2];      // + 2: a half warp's 8-byte stores miss one another
     const int seq = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * GLA_COLS;
     const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
     if (t1 <= t0) return;
