@@ -363,14 +363,14 @@ def parunex_config(size: dict) -> dict:
     gated feed-forward and the others with eight experts of half that width, two per token (the same active
     feed-forward parameters as the dense one)."""
     w, h = size["width"], size["width"] // 128
-    rot = {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 4096}}
+    rot = {"base": 1000000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 6.0, "original": 4096}}
     dense = {"kind": "dense", "ff": size["ff"]}
     routed = {"kind": "moe", "expert": {"ff": size["ff"] // 2},
-              "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 2}, "scale": 2.0}}
+              "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 2}, "scale": 2.5}}
     attention = {"type": "attention",
-                 "mixer": {"heads": h, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 50.0,
+                 "mixer": {"heads": h, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
                            "v_mix": True, "rot": rot}}
-    recurrence = {"type": "gla", "mixer": {"heads": h, "dim": 128, "vdim": 128, "tau": 16.0}}
+    recurrence = {"type": "gla", "mixer": {"heads": h, "dim": 128, "vdim": 128, "tau": 8.0}}
     layers = [dict(attention if i % 2 == 0 else recurrence, mlp=dense if i == 0 else routed)
               for i in range(COMPARE_LAYERS)]
     return {"architecture": "Parunex", "vocab": COMPARE_VOCAB, "width": w, "embedding": {"scale": 1.0},

@@ -50,8 +50,8 @@ class ParunexRotary:
     dims: int
     base: float
     factor: float | None = None
-    low: float = 1.0
-    high: float = 4.0
+    low: float = 0.0
+    high: float = 0.0
     original: float = 0.0
 
     @classmethod
@@ -200,7 +200,7 @@ class ParunexConfig:
 
     architecture = "Parunex"
     model_type = "parunex"
-    DEFAULT_DECAY_RANK = 16
+    DEFAULT_DECAY_RANK = 32
 
     @property
     def vocab_size(self) -> int:

@@ -262,8 +262,8 @@ class WavelengthRotarySpec:
     theta: float
     factor: float | None = None
     original: float = 0.0
-    low: float = 1.0
-    high: float = 4.0
+    low: float = 0.0
+    high: float = 0.0
     kind: str = "rotary_wavelength"
 
     def __post_init__(self) -> None:

@@ -60,9 +60,9 @@ MODEL_P = model(96, 300, 3.0, [
 # layers mixing values, a top-1 router, rotation over the whole head and over none of it
 MODEL_Q = model(128, 257, 1.0, [
     attention(8, 2, 64, 64, 0.125, 30.0, 64, v_mix=True, mlp=moe(96, 4, 1, 2, 1, scale=2.5)),
-    gla(2, 64, 64, 16.0, mlp=None),
+    gla(2, 64, 64, 12.0, mlp=None),
     attention(4, 2, 128, 64, 0.09, 10.0, 0, v_mix=True, mlp=dense(256)),
-    attention(2, 2, 64, 64, 0.125, 50.0, 16, v_mix=True, scaling={"factor": 2.0, "low": 2.0, "high": 8.0,
+    attention(2, 2, 64, 64, 0.125, 45.0, 16, v_mix=True, scaling={"factor": 2.0, "low": 2.0, "high": 8.0,
                                                                   "original": 64}, mlp=None),
     gla(1, 128, 32, 2.0, mlp=moe(64, 9, 4, 3, 2)),
 ], ranks=[0, 32, 0, 0, 3])
@@ -75,7 +75,7 @@ MODEL_R = model(100, 131, 7.5, [
 
 # a middle size for long prompts: products of more than a thousand rows, 128-wide heads in a group of two
 MODEL_S = model(256, 640, 2.0, [
-    attention(4, 2, 128, 128, 0.09, 25.0, 64, v_mix=True, scaling={"factor": 4.0, "low": 1.0, "high": 4.0,
+    attention(4, 2, 128, 128, 0.09, 25.0, 64, v_mix=True, scaling={"factor": 6.0, "low": 1.0, "high": 3.0,
                                                                    "original": 256}, mlp=moe(128, 8, 2, 4, 2, 1.5)),
     gla(4, 64, 64, 8.0, mlp=dense(384)),
     attention(4, 2, 128, 128, 0.09, 25.0, 64, v_mix=True, mlp=dense(256)),

@@ -330,7 +330,7 @@ def test_recurrence_kernels_continue_from_their_state(heads, dim, vdim, rank):
 
 
 # ---------------------------------------------------------------------- each mechanism alone, as a model of one layer
-SCALING = {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 32}
+SCALING = {"factor": 3.0, "low": 1.0, "high": 5.0, "original": 32}
 LAYERS_ALONE = {
     "attention_narrow_values": (attention(4, 2, 24, 8, 0.3, 9.0, 12, scaling=SCALING), None),
     "attention_wide_values": (attention(3, 1, 8, 24, 0.35, 2.5, 8, base=50.0), None),
