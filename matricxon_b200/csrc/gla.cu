@@ -66,19 +66,21 @@ __global__ void __launch_bounds__(GLA_THREADS)
 gla_scan_kernel(const float* __restrict__ proj, int ld, int q_col, int k_col, int v_col, const float* __restrict__ decay,
                 float q_scale, float* __restrict__ state, const int* __restrict__ cu_q, const int* __restrict__ state_slots,
                 float* __restrict__ out, int n_heads, int dim, int vdim) {
-    // a thread's ROWS channels lie side by side, four floats of padding behind them: the 16-byte loads of the
-    // eight slices of a quarter warp then fall on different banks
+    // a thread's ROWS channels lie side by side (four floats of padding keep the rows of neighbouring slices on
+    // different banks)
     constexpr int PAD = ROWS + 4, R4 = ROWS / 4, CH = GLA_SLICES * ROWS;
     __shared__ __align__(16) float q_s[GLA_TOKENS][GLA_SLICES][PAD], k_s[GLA_TOKENS][GLA_SLICES][PAD],
         a_s[GLA_TOKENS][GLA_SLICES][PAD];
     __shared__ __align__(8) float v_s[GLA_TOKENS][GLA_COLS];
     // a thread's share of every output of the round; the sixteen shares of an output are added up once a round
     // (a shuffle chain per token would be the longest wait of the loop)
-    __shared__ __align__(8) float o_s[GLA_TOKENS][GLA_SLICES][GLA_COLS + 2];      // + 2: a half warp's 8-byte stores miss one another
+    __shared__ __align__(8) float o_s[GLA_TOKENS][GLA_SLICES][GLA_COLS];
     const int seq = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * GLA_COLS;
     const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
     if (t1 <= t0) return;
-    const int tid = threadIdx.x, slice = tid & (GLA_SLICES - 1), pair = tid / GLA_SLICES, col = col0 + 2 * pair;
+    // the eight column pairs of a slice are neighbouring lanes: a warp's state accesses are whole 64-byte row pieces,
+    // its operand loads from shared memory are broadcasts
+    const int tid = threadIdx.x, pair = tid & (GLA_COLS / 2 - 1), slice = tid / (GLA_COLS / 2), col = col0 + 2 * pair;
     float* s_base = state + (((size_t)state_slots[seq] * n_heads + head) * dim) * vdim;
     float S0[ROWS], S1[ROWS];          // this thread's channels of columns col and col + 1
 #pragma unroll
