@@ -8,8 +8,9 @@
 //   every key channel, decay[t][c] = exp(log_sigmoid(A2[c] . low[t] + b[c]) / tau); A2 is float [channels][rank].
 //   The small second product stays on the FP32 cores so that no rounding enters the decay.
 // mx_gla_scan: every sequence's tokens in order, from and to the state slot [heads][dim][vdim] of the sequence.
-//   A block owns (sequence, head, 16 value columns); a thread owns two columns and a sixteenth of their key
-//   channels (decay, key and query of a channel serve both columns), so the state stays in registers for the whole
+//   A block owns (sequence, head, 16 value columns); a thread owns two columns and a sixteenth or a thirty-second
+//   of their key channels (decay, key and query of a channel serve both columns; four or eight state rows a thread,
+//   so that an SM holds eight warps of a head's 16,384 state elements), and the state stays in registers for the whole
 //   portion. Tokens arrive eight or sixteen at a time through shared memory; a thread's operands of the next token are in
 //   registers before it computes the current one, and the shares of an output are added up once a round.
 //   q is scaled by `q_scale` on its way in. Columns of a state are independent of one another, so cutting vdim
@@ -23,8 +24,6 @@
 namespace {
 
 constexpr int GLA_COLS = 16;       // value columns per block
-constexpr int GLA_SLICES = 16;     // threads per pair of columns, each with a sixteenth of the key channels
-constexpr int GLA_THREADS = GLA_COLS / 2 * GLA_SLICES;
 
 __global__ void __launch_bounds__(256)
 gla_decay_kernel(const float* __restrict__ low, int low_ld, const float* __restrict__ a2, const float* __restrict__ bias,
@@ -61,18 +60,21 @@ gla_decay_kernel(const float* __restrict__ low, int low_ld, const float* __restr
     decay[(size_t)t * channels + c] = expf(log_sig * inv_tau);
 }
 
-template <int ROWS, int GLA_TOKENS>     // key channels per thread: dim <= 16 * ROWS; tokens staged per round
-__global__ void __launch_bounds__(GLA_THREADS)
+// GLA_SLICES threads share a pair of columns, each with ROWS of the key channels (dim <= GLA_SLICES * ROWS);
+// GLA_TOKENS tokens are staged per round
+template <int ROWS, int GLA_SLICES, int GLA_TOKENS>
+__global__ void __launch_bounds__(GLA_COLS / 2 * GLA_SLICES)
 gla_scan_kernel(const float* __restrict__ proj, int ld, int q_col, int k_col, int v_col, const float* __restrict__ decay,
                 float q_scale, float* __restrict__ state, const int* __restrict__ cu_q, const int* __restrict__ state_slots,
                 float* __restrict__ out, int n_heads, int dim, int vdim) {
     // a thread's ROWS channels lie side by side (four floats of padding keep the rows of neighbouring slices on
     // different banks)
+    constexpr int GLA_THREADS = GLA_COLS / 2 * GLA_SLICES;
     constexpr int PAD = ROWS + 4, R4 = ROWS / 4, CH = GLA_SLICES * ROWS;
     __shared__ __align__(16) float q_s[GLA_TOKENS][GLA_SLICES][PAD], k_s[GLA_TOKENS][GLA_SLICES][PAD],
         a_s[GLA_TOKENS][GLA_SLICES][PAD];
     __shared__ __align__(8) float v_s[GLA_TOKENS][GLA_COLS];
-    // a thread's share of every output of the round; the sixteen shares of an output are added up once a round
+    // a thread's share of every output of the round; the shares of an output are added up once a round
     // (a shuffle chain per token would be the longest wait of the loop)
     __shared__ __align__(8) float o_s[GLA_TOKENS][GLA_SLICES][GLA_COLS];
     const int seq = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * GLA_COLS;
@@ -92,7 +94,7 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_col, int k_col, in
     // A round's tokens travel global memory -> registers -> shared memory; the registers of the next round are
     // asked for before this round is computed, so that the recurrence never waits for global memory.
     constexpr int PER = GLA_TOKENS * CH / GLA_THREADS;             // (token, channel) items a thread stages per array
-    constexpr int V_PER = GLA_TOKENS * GLA_COLS / GLA_THREADS;
+    constexpr int V_PER = (GLA_TOKENS * GLA_COLS + GLA_THREADS - 1) / GLA_THREADS;
     float q_r[PER], k_r[PER], a_r[PER], v_r[V_PER];
     auto fetch = [&](int base) {
         const int n_here = min(GLA_TOKENS, t1 - base);
@@ -108,7 +110,8 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_col, int k_col, in
 #pragma unroll
         for (int u = 0; u < V_PER; ++u) {
             const int item = tid + u * GLA_THREADS, j = item / GLA_COLS, c = item % GLA_COLS;
-            v_r[u] = (j < n_here && col0 + c < vdim) ? proj[(size_t)(base + j) * ld + v_col + head * vdim + col0 + c] : 0.f;
+            v_r[u] = (item < GLA_TOKENS * GLA_COLS && j < n_here && col0 + c < vdim)
+                         ? proj[(size_t)(base + j) * ld + v_col + head * vdim + col0 + c] : 0.f;
         }
     };
     // one token's operands of this thread, from shared memory into registers (asked for one token ahead)
@@ -161,7 +164,7 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_col, int k_col, in
 #pragma unroll
         for (int u = 0; u < V_PER; ++u) {
             const int item = tid + u * GLA_THREADS;
-            v_s[item / GLA_COLS][item % GLA_COLS] = v_r[u];
+            if (item < GLA_TOKENS * GLA_COLS) v_s[item / GLA_COLS][item % GLA_COLS] = v_r[u];
         }
         __syncthreads();
         if (base + GLA_TOKENS < t1) fetch(base + GLA_TOKENS);
@@ -246,13 +249,13 @@ extern "C" int mx_gla_scan(const float* proj, int ld, int q_col, int k_col, int 
     if (n_heads > 65535 || vdim > 65535 * GLA_COLS) MX_REFUSE("gated linear attention: %d heads of %d values exceed the grid", n_heads, vdim);
     const dim3 grid(n_seqs, n_heads, (vdim + GLA_COLS - 1) / GLA_COLS);
     if (dim <= 64)
-        gla_scan_kernel<4, 16><<<grid, GLA_THREADS, 0, stream>>>(proj, ld, q_col, k_col, v_col, decay, q_scale, state, cu_q,
+        gla_scan_kernel<4, 16, 16><<<grid, 128, 0, stream>>>(proj, ld, q_col, k_col, v_col, decay, q_scale, state, cu_q,
                                                             state_slots, out, n_heads, dim, vdim);
     else if (dim <= 128)
-        gla_scan_kernel<8, 8><<<grid, GLA_THREADS, 0, stream>>>(proj, ld, q_col, k_col, v_col, decay, q_scale, state, cu_q,
+        gla_scan_kernel<4, 32, 8><<<grid, 256, 0, stream>>>(proj, ld, q_col, k_col, v_col, decay, q_scale, state, cu_q,
                                                              state_slots, out, n_heads, dim, vdim);
     else
-        gla_scan_kernel<16, 8><<<grid, GLA_THREADS, 0, stream>>>(proj, ld, q_col, k_col, v_col, decay, q_scale, state, cu_q,
+        gla_scan_kernel<16, 16, 8><<<grid, 128, 0, stream>>>(proj, ld, q_col, k_col, v_col, decay, q_scale, state, cu_q,
                                                              state_slots, out, n_heads, dim, vdim);
     return mx_launch_status();
 }
