@@ -6,7 +6,8 @@
 //
 // mx_gla_decay: rows `low` (the float result of the A1 projection, `rank` wide, `low_ld` apart) -> the decay of
 //   every key channel, decay[t][c] = exp(log_sigmoid(A2[c] . low[t] + b[c]) / tau); A2 is float [channels][rank].
-//   The small second product stays on the FP32 cores so that no rounding enters the decay.
+//   The small second product stays on the FP32 cores so that no rounding enters the decay: a thread per channel
+//   keeps its row of A2 in registers for sixteen tokens.
 // mx_gla_scan: every sequence's tokens in order, from and to the state slot [heads][dim][vdim] of the sequence.
 //   A block owns (sequence, head, 16 value columns); a thread owns two columns and a sixteenth or a thirty-second
 //   of their key channels (decay, key and query of a channel serve both columns; four or eight state rows a thread,
@@ -25,39 +26,65 @@ namespace {
 
 constexpr int GLA_COLS = 16;       // value columns per block
 
+constexpr int DECAY_TOKENS = 16;   // tokens a block of the decay kernel walks with its rows of A2 in registers
+constexpr int DECAY_CHUNK = 32;    // entries of a row of A2 a thread holds at a time
+
 __global__ void __launch_bounds__(256)
 gla_decay_kernel(const float* __restrict__ low, int low_ld, const float* __restrict__ a2, const float* __restrict__ bias,
-                 float inv_tau, float* __restrict__ decay, int channels, int rank) {
-    extern __shared__ float low_s[];
-    const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
-    for (int r = threadIdx.x; r < rank; r += blockDim.x) low_s[r] = low[(size_t)t * low_ld + r];
+                 float inv_tau, float* __restrict__ decay, int n_tokens, int channels, int rank, int rank_pad) {
+    // a thread owns one channel: its row of A2 is read once for DECAY_TOKENS tokens, whose low-rank vectors lie in
+    // shared memory (padded with zeros to a multiple of four) and are read as broadcasts
+    extern __shared__ __align__(16) float low_s[];           // [DECAY_TOKENS][rank_pad]
+    const int t0 = blockIdx.x * DECAY_TOKENS, n_here = min(DECAY_TOKENS, n_tokens - t0);
+    for (int item = threadIdx.x; item < DECAY_TOKENS * rank_pad; item += blockDim.x) {
+        const int j = item / rank_pad, r = item - j * rank_pad;
+        low_s[item] = (j < n_here && r < rank) ? low[(size_t)(t0 + j) * low_ld + r] : 0.f;
+    }
     __syncthreads();
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= channels) return;
     const float* w = a2 + (size_t)c * rank;
-    float z = bias ? bias[c] : 0.f;
-    if (rank % 4 == 0 && (reinterpret_cast<uintptr_t>(a2) & 15) == 0) {
-        // the row's loads set out together
-        for (int r = 0; r < rank; r += 16) {
-            float4 w4[4];
+    const bool vec = rank % 4 == 0 && (reinterpret_cast<uintptr_t>(a2) & 15) == 0;
+    float z[DECAY_TOKENS];
+    const float b = bias ? bias[c] : 0.f;
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-                w4[u] = (r + 4 * u < rank) ? *reinterpret_cast<const float4*>(w + r + 4 * u) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < DECAY_TOKENS; ++j) z[j] = b;
+    for (int r0 = 0; r0 < rank; r0 += DECAY_CHUNK) {
+        float4 w4[DECAY_CHUNK / 4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                if (r + 4 * u < rank) {
-                    z = fmaf(w4[u].x, low_s[r + 4 * u], z);
-                    z = fmaf(w4[u].y, low_s[r + 4 * u + 1], z);
-                    z = fmaf(w4[u].z, low_s[r + 4 * u + 2], z);
-                    z = fmaf(w4[u].w, low_s[r + 4 * u + 3], z);
+        for (int u = 0; u < DECAY_CHUNK / 4; ++u) {
+            const int r = r0 + 4 * u;
+            if (vec) {
+                w4[u] = r < rank ? *reinterpret_cast<const float4*>(w + r) : make_float4(0.f, 0.f, 0.f, 0.f);
+            } else {
+                w4[u].x = r < rank ? w[r] : 0.f;
+                w4[u].y = r + 1 < rank ? w[r + 1] : 0.f;
+                w4[u].z = r + 2 < rank ? w[r + 2] : 0.f;
+                w4[u].w = r + 3 < rank ? w[r + 3] : 0.f;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < DECAY_TOKENS; ++j) {
+#pragma unroll
+            for (int u = 0; u < DECAY_CHUNK / 4; ++u) {
+                if (r0 + 4 * u < rank_pad) {
+                    const float4 l4 = *reinterpret_cast<const float4*>(&low_s[j * rank_pad + r0 + 4 * u]);
+                    z[j] = fmaf(w4[u].x, l4.x, z[j]);
+                    z[j] = fmaf(w4[u].y, l4.y, z[j]);
+                    z[j] = fmaf(w4[u].z, l4.z, z[j]);
+                    z[j] = fmaf(w4[u].w, l4.w, z[j]);
                 }
             }
         }
-    } else {
-        for (int r = 0; r < rank; ++r) z = fmaf(w[r], low_s[r], z);
     }
-    // log(sigmoid(z)) without cancellation on either side
-    const float log_sig = z >= 0.f ? -log1pf(expf(-z)) : z - log1pf(expf(z));
-    decay[(size_t)t * channels + c] = expf(log_sig * inv_tau);
+#pragma unroll
+    for (int j = 0; j < DECAY_TOKENS; ++j) {
+        if (j < n_here) {
+            // log(sigmoid(z)) without cancellation on either side
+            const float log_sig = z[j] >= 0.f ? -log1pf(expf(-z[j])) : z[j] - log1pf(expf(z[j]));
+            decay[(size_t)(t0 + j) * channels + c] = expf(log_sig * inv_tau);
+        }
+    }
 }
 
 // GLA_SLICES threads share a pair of columns, each with ROWS of the key channels (dim <= GLA_SLICES * ROWS);
@@ -235,9 +262,11 @@ extern "C" int mx_gla_decay(const float* low, int low_ld, const float* a2, const
                             int n_tokens, int channels, int rank, cudaStream_t stream) {
     if (n_tokens <= 0) return MX_OK;
     if (!(tau > 0.f)) MX_REFUSE("gated linear attention: tau %f is not positive", tau);
-    if (rank <= 0 || rank > 8192) MX_REFUSE("gated linear attention: a decay rank of %d", rank);
-    gla_decay_kernel<<<dim3(n_tokens, (channels + 255) / 256), 256, (size_t)rank * sizeof(float), stream>>>(
-        low, low_ld, a2, bias, 1.0f / tau, decay, channels, rank);
+    const int rank_pad = (rank + 3) & ~3;
+    const size_t smem = (size_t)DECAY_TOKENS * rank_pad * sizeof(float);
+    if (rank <= 0 || smem > 48 * 1024) MX_REFUSE("gated linear attention: a decay rank of %d (1..768)", rank);
+    gla_decay_kernel<<<dim3((n_tokens + DECAY_TOKENS - 1) / DECAY_TOKENS, (channels + 255) / 256), 256, smem, stream>>>(
+        low, low_ld, a2, bias, 1.0f / tau, decay, n_tokens, channels, rank, rank_pad);
     return mx_launch_status();
 }
 

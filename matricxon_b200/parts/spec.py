@@ -353,6 +353,8 @@ class GlaSpec:
             raise ValueError("gated linear attention needs positive head count, head sizes and decay rank")
         if self.head_dim > 256:
             raise ValueError(f"{self.head_dim} key channels per head: the recurrence kernel takes up to 256")
+        if self.decay_rank > 768:
+            raise ValueError(f"a decay rank of {self.decay_rank}: the decay kernel takes up to 768")
         if not self.tau > 0:
             raise ValueError(f"tau must be positive, got {self.tau}")
 
