@@ -330,12 +330,33 @@ attention_mma_kernel(const MmaAttnParams p) {
             }
         const float scale_log2 = p.cap_log2 > 0.f ? 1.f : p.scale_log2;
         if (p.cap_log2 > 0.f) {
+            // small arguments (the usual case) take the polynomial; one large score in the warp's chunk sends
+            // the whole warp through the exponential form
+            float largest = 0.f;
 #pragma unroll
             for (int ch = 0; ch < NCH; ++ch)
 #pragma unroll
                 for (int b = 0; b < 4; ++b)
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) s[ch][b][e] = p.cap_log2 * tanh_by_exp2(s[ch][b][e] * p.cap_in);
+                    for (int e = 0; e < 4; ++e) {
+                        s[ch][b][e] *= p.cap_in;
+                        largest = fmaxf(largest, fabsf(s[ch][b][e]));
+                    }
+            if (__all_sync(0xffffffffu, largest <= TANH_SMALL)) {
+#pragma unroll
+                for (int ch = 0; ch < NCH; ++ch)
+#pragma unroll
+                    for (int b = 0; b < 4; ++b)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) s[ch][b][e] = p.cap_log2 * tanh_small(s[ch][b][e]);
+            } else {
+#pragma unroll
+                for (int ch = 0; ch < NCH; ++ch)
+#pragma unroll
+                    for (int b = 0; b < 4; ++b)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) s[ch][b][e] = p.cap_log2 * tanh_by_exp2(s[ch][b][e]);
+            }
         }
         // mask (only where the chunks cross an edge), running max and sum for rows g, g + 8
         float m_new[2] = {m_run[0], m_run[1]};

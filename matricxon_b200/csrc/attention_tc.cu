@@ -476,8 +476,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
                 tmem_load32(s_addr + 64 * part + 32, sc + 32);
                 asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
                 if (p.cap_log2 > 0.f) {
+                    // small arguments (the usual case) take the polynomial on the FMA pipe; one large score among
+                    // the warp's rows sends the whole warp through the exponential form
+                    float largest = 0.f;
 #pragma unroll
-                    for (int c = 0; c < 64; ++c) sc[c] = p.cap_log2 * tanh_by_exp2(sc[c] * p.cap_in);
+                    for (int c = 0; c < 64; ++c) {
+                        sc[c] *= p.cap_in;
+                        largest = fmaxf(largest, fabsf(sc[c]));
+                    }
+                    if (__all_sync(0xffffffffu, largest <= TANH_SMALL)) {
+#pragma unroll
+                        for (int c = 0; c < 64; ++c) sc[c] = p.cap_log2 * tanh_small(sc[c]);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 64; ++c) sc[c] = p.cap_log2 * tanh_by_exp2(sc[c]);
+                    }
                 }
                 if (edge) {
 #pragma unroll

@@ -124,6 +124,20 @@ __device__ __forceinline__ float tanh_by_exp2(float x) {
     return 1.f - __fdividef(2.f, 1.f + e);
 }
 
+// tanh of a small argument on the FMA pipe: the odd Taylor polynomial up to x^11, whose first dropped term is
+// below 2e-8 of x for |x| <= TANH_SMALL. Scores under a cap are mostly that small (|score| <= 0.35 cap), and the
+// special-function units that tanh_by_exp2 needs are what bounds a softmax.
+#define TANH_SMALL 0.35f
+__device__ __forceinline__ float tanh_small(float x) {
+    const float x2 = x * x;
+    float p = -1382.f / 155925.f;
+    p = fmaf(p, x2, 62.f / 2835.f);
+    p = fmaf(p, x2, -17.f / 315.f);
+    p = fmaf(p, x2, 2.f / 15.f);
+    p = fmaf(p, x2, -1.f / 3.f);
+    return fmaf(x * x2, p, x);
+}
+
 // tanh-approximated GELU: 0.5 u (1 + tanh(sqrt(2/pi) (u + 0.044715 u^3))).
 __device__ __forceinline__ float gelu_tanh(float u) {
     const float k0 = 0.7978845608028654f, k1 = 0.044715f;

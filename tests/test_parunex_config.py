@@ -242,3 +242,18 @@ def test_plain_model_is_independent_of_what_follows():
     used = dict(tensors)
     used["l4.mix.vmix"] = torch.tensor(0.99)
     assert not torch.allclose(plain.forward(raw, used, tokens), whole, atol=1e-4)
+
+
+def test_benchmark_configurations_describe_runnable_models():
+    """The sizes ``bench.py --compare parunex`` times: they parse, name every tensor once, and plan one cache group
+    and a state per recurrent layer."""
+    import bench
+
+    for size in bench.COMPARE_SIZES.values():
+        config = config_from_dict(bench.parunex_config(size))
+        spec = config.model_spec()
+        names = [s.name for s in model_weight_specs(spec)]
+        assert len(names) == len(set(names))
+        plan = plan_cache(spec)
+        assert len(plan.groups) == 1 and plan.groups[0].request.head_dim == 128
+        assert sum(s is not None for s in plan.state_of_entry) == bench.COMPARE_LAYERS // 2
