@@ -286,6 +286,25 @@ __global__ void moe_combine_sorted_kernel(const float* __restrict__ rows, const 
     residual[i] += sum;
 }
 
+// the same, four columns a thread (width a multiple of 4, 16-byte aligned rows)
+__global__ void moe_combine_sorted_vec_kernel(const float* __restrict__ rows, const int* __restrict__ ids,
+                                              const int* __restrict__ place, const int* __restrict__ first,
+                                              const float* __restrict__ weight, float* __restrict__ residual, int top,
+                                              int width4, long long count) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const long long t = i / width4;
+    const int c = (int)(i - t * width4);
+    float4 sum = reinterpret_cast<const float4*>(residual)[i];
+    for (int s = 0; s < top; ++s) {
+        const long long pair = t * top + s;
+        const float w = weight[pair];
+        const float4 v = reinterpret_cast<const float4*>(rows)[((size_t)first[ids[pair]] + place[pair]) * width4 + c];
+        sum.x = fmaf(w, v.x, sum.x); sum.y = fmaf(w, v.y, sum.y); sum.z = fmaf(w, v.z, sum.z); sum.w = fmaf(w, v.w, sum.w);
+    }
+    reinterpret_cast<float4*>(residual)[i] = sum;
+}
+
 template <typename T>
 __global__ void glu_kernel(const T* __restrict__ gu, int ld, T* __restrict__ out, int ff, int act, long long count) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -398,6 +417,12 @@ extern "C" int mx_moe_combine_sorted(const float* rows, const int* ids, const in
                                      cudaStream_t stream) {
     const long long count = (long long)n_tokens * width;
     if (count <= 0) return MX_OK;
+    if (width % 4 == 0 && ((uintptr_t)rows | (uintptr_t)residual) % 16 == 0) {
+        const long long count4 = count / 4;
+        moe_combine_sorted_vec_kernel<<<(unsigned)((count4 + 255) / 256), 256, 0, stream>>>(
+            rows, ids, place, first, weight, residual, top, width / 4, count4);
+        return mx_launch_status();
+    }
     moe_combine_sorted_kernel<<<(unsigned)((count + 255) / 256), 256, 0, stream>>>(rows, ids, place, first, weight,
                                                                                    residual, top, width, count);
     return mx_launch_status();

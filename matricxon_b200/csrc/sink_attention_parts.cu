@@ -86,6 +86,25 @@ __global__ void head_gate_kernel(const T* __restrict__ attn, const float* __rest
     out[i] = from_float<T>(a * sigmoid_exact(gate[(size_t)t * gate_ld + h]));
 }
 
+// eight neighbouring values a thread, 16-byte accesses (bfloat16, vdim and hd multiples of 8)
+__global__ void head_gate_vec_kernel(const __nv_bfloat16* __restrict__ attn, const float* __restrict__ gate, int gate_ld,
+                                     __nv_bfloat16* __restrict__ out, int n_heads, int vdim, int hd, long long groups) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= groups) return;
+    const int per_row = n_heads * vdim / 8;
+    const long long t = i / per_row;
+    const int c = (int)(i - t * per_row) * 8;
+    const int h = c / vdim, e = c - h * vdim;
+    const float g = sigmoid_exact(gate[(size_t)t * gate_ld + h]);
+    const uint4 raw = *reinterpret_cast<const uint4*>(attn + ((size_t)t * n_heads + h) * hd + e);
+    const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    uint4 oraw;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&oraw);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) o2[k] = __floats2bfloat162_rn(__low2float(a2[k]) * g, __high2float(a2[k]) * g);
+    *reinterpret_cast<uint4*>(out + (size_t)t * n_heads * vdim + c) = oraw;
+}
+
 }  // namespace
 
 extern "C" int mx_rotate_mix_kv_write(const float* proj, int ld, const int* positions, const float* freq, int rot,
@@ -117,6 +136,12 @@ extern "C" int mx_head_gate(const void* attn, const float* gate, int gate_ld, vo
     const long long count = (long long)n_tokens * n_heads * vdim;
     if (count <= 0) return MX_OK;
     const unsigned blocks = (unsigned)((count + 255) / 256);
+    if (dtype == MX_DTYPE_BF16 && vdim % 8 == 0 && hd % 8 == 0 && ((uintptr_t)attn | (uintptr_t)out) % 16 == 0) {
+        const long long groups = count / 8;
+        head_gate_vec_kernel<<<(unsigned)((groups + 255) / 256), 256, 0, stream>>>(
+            (const __nv_bfloat16*)attn, gate, gate_ld, (__nv_bfloat16*)out, n_heads, vdim, hd, groups);
+        return mx_launch_status();
+    }
     if (dtype == MX_DTYPE_F32)
         head_gate_kernel<float><<<blocks, 256, 0, stream>>>((const float*)attn, gate, gate_ld, (float*)out, n_heads,
                                                            vdim, hd, count);
