@@ -197,6 +197,10 @@ class ParunexConfig:
     # configuration alone (random weights); a model folder's tensors overrule it (``with_tensor_shapes``).
     decay_ranks: tuple[int, ...] = ()
     max_positions: int = DEFAULT_MAX_POSITIONS
+    # tensors a model folder holds although the model does not use them (a mixing scalar of a layer that does not
+    # mix, the second norm of a layer without a feed-forward): (name, shape), found by ``with_tensor_shapes``; they
+    # are expected at the weight check and never fetched
+    unused_tensors: tuple[tuple[str, tuple[int, ...]], ...] = ()
 
     architecture = "Parunex"
     model_type = "parunex"
@@ -240,14 +244,24 @@ class ParunexConfig:
         """The configuration with every gla layer's decay rank read from its tensors: ``shape_of(name)`` gives a
         tensor's shape or None."""
         ranks = list(self.decay_ranks)
+        unused = []
         for index, layer in enumerate(self.layers):
             if layer.type == "gla":
                 shape = shape_of(f"l{index}.mix.a1")
                 if shape is not None and len(shape) == 2:
                     ranks[index] = int(shape[0])
+            optional = []
+            if layer.type == "attention" and not layer.v_mix:
+                optional.append(f"l{index}.mix.vmix")
+            if layer.feed_forward is None:
+                optional += [f"l{index}.norm2", f"l{index}.norm2.b", f"l{index}.norm2.alpha"]
+            for name in optional:
+                shape = shape_of(name)
+                if shape is not None:
+                    unused.append((name, tuple(int(extent) for extent in shape)))
         from dataclasses import replace
 
-        return replace(self, decay_ranks=tuple(ranks))
+        return replace(self, decay_ranks=tuple(ranks), unused_tensors=tuple(unused))
 
     def to_dict(self) -> dict[str, Any]:
         out = {"architecture": self.architecture, "embedding": {"scale": self.embedding_scale},
@@ -275,7 +289,7 @@ class ParunexConfig:
                 hidden_size=self.width, num_heads=layer.heads, num_kv_heads=layer.kv_heads, head_dim=layer.dim,
                 value_dim=layer.vdim, window=None, scale=layer.scale, softcap=layer.softcap, bias=True,
                 position=position, query_name="q", key_name="k", value_name="v", output_name="o", gate_name="g",
-                sink_name="sink", value_mix=value_mix, value_mix_name="vmix", bias_suffix=".b")
+                sink_name="sink", value_mix=value_mix, value_mix_name="vmix" if layer.v_mix else None, bias_suffix=".b")
         return GlaSpec(hidden_size=self.width, num_heads=layer.heads, head_dim=layer.dim, value_dim=layer.vdim,
                        decay_rank=self.decay_ranks[index] or self.DEFAULT_DECAY_RANK, tau=layer.tau,
                        query_scale=layer.dim ** -0.5, eps=self.eps, query_name="q", key_name="k", value_name="v",
@@ -311,4 +325,5 @@ class ParunexConfig:
             schedule=sequential_schedule(len(layers)), final_norm=norm, tie_word_embeddings=False,
             max_position_embeddings=self.max_positions, embedding_name="embed", layer_prefix="l",
             final_norm_name="final.norm", head_name="head", embedding_scale=self.embedding_scale, weight_suffix="",
-            layer_prefix_format="{prefix}{index}.", final_norm_prefix="final.norm")
+            layer_prefix_format="{prefix}{index}.", final_norm_prefix="final.norm",
+            extra={"unused_tensors": self.unused_tensors})

@@ -69,6 +69,9 @@ def model_weight_specs(spec: ModelSpec) -> list[WeightSpec]:
                                 role="matrix", init="weight"))
     if spec.head_bias:
         specs.append(WeightSpec(f"{spec.head_name}.bias", (spec.vocab_size,), role="vector", init="bias"))
+    # tensors that an architecture knows to lie in its model folders without being used: expected, never fetched
+    for name, shape in spec.extra.get("unused_tensors", ()):
+        specs.append(WeightSpec(name, tuple(shape), role="vector", init="bias"))
     return specs
 
 

@@ -301,7 +301,7 @@ class SinkAttentionSpec:
     gate_name: str | None = None
     sink_name: str | None = None
     value_mix: str | None = None              # None | "source" | "blend"
-    value_mix_name: str | None = None         # the scalar's tensor; declared for every layer that names it
+    value_mix_name: str | None = None         # the scalar's tensor; declared (and read) where it is named
     value_mix_key: str = "value_mix"
     bias_suffix: str = ".b"
     kind: str = "sink_attention"

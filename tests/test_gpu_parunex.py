@@ -549,6 +549,10 @@ def test_trace_program_and_command_line(tmp_path):
     raw = copy.deepcopy(MODELS["Q"])
     tensors = draw(raw, seed=12, sharpen=2.0, store_dtype=torch.bfloat16)
     del raw["decay_ranks"]                          # a model folder's config.json does not name them
+    # a file may hold the second norm of a layer that has no feed-forward: expected, unused
+    tensors["l1.norm2"] = torch.ones(128, dtype=torch.bfloat16)
+    tensors["l1.norm2.b"] = torch.zeros(128, dtype=torch.bfloat16)
+    tensors["l1.norm2.alpha"] = torch.tensor(1.0, dtype=torch.bfloat16)
     folder = tmp_path / "model"
     folder.mkdir()
     (folder / "config.json").write_text(json.dumps(raw))

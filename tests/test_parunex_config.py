@@ -45,6 +45,7 @@ def test_tensor_names_shapes_and_cache_plan():
     assert shapes["l1.mix.q"] == (144, 96) and shapes["l1.mix.q.b"] == (144,) and shapes["l1.mix.k"] == (72, 96)
     assert shapes["l1.mix.v"] == (48, 96) and shapes["l1.mix.v.b"] == (48,) and shapes["l1.mix.g"] == (6, 96)
     assert shapes["l1.mix.sink"] == (6,) and shapes["l1.mix.vmix"] == () and shapes["l1.mix.o"] == (96, 96)
+    assert "l2.mix.vmix" not in shapes and shapes["l4.mix.vmix"] == ()      # only layers that mix name the scalar
     assert "l1.mix.g.b" not in shapes and "l1.mix.o.b" not in shapes
     assert shapes["l1.mlp.gate"] == (136, 96) and shapes["l1.mlp.down"] == (96, 136)
     # layer 2 has no feed-forward and so no second norm
@@ -139,7 +140,7 @@ def test_frequency_table_against_the_plain_one(rot):
 
 # ---------------------------------------------------------------------------- properties of the plain model
 def _attention_setup(seed=0, T=12):
-    layer = attention(4, 2, 16, 8, 0.3, 5.0, 8)
+    layer = attention(4, 2, 16, 8, 0.3, 5.0, 8, v_mix=True)
     raw = single_layer(layer)
     tensors = {k: v.to(F64) for k, v in draw(raw, seed, sharpen=3.0).items()}
     h = torch.randn(T, 64, dtype=F64, generator=torch.Generator().manual_seed(seed))
@@ -257,3 +258,25 @@ def test_benchmark_configurations_describe_runnable_models():
         plan = plan_cache(spec)
         assert len(plan.groups) == 1 and plan.groups[0].request.head_dim == 128
         assert sum(s is not None for s in plan.state_of_entry) == bench.COMPARE_LAYERS // 2
+
+
+def test_tensors_that_lie_unused_in_a_model_folder_are_expected():
+    """A mixing scalar of a layer that does not mix and the second norm of a layer without a feed-forward may be
+    in a file: the configuration learns of them from the tensors and the weight check lets them pass."""
+    raw = MODELS["P"]
+    tensors = draw(raw, 1)
+    config = config_from_dict(copy.deepcopy(raw))
+    extra = dict(tensors)
+    extra["l2.mix.vmix"] = torch.tensor(0.5)
+    extra["l2.norm2"] = torch.ones(96)
+    extra["l2.norm2.b"] = torch.zeros(96)
+    extra["l2.norm2.alpha"] = torch.tensor(1.0)
+    with pytest.raises(WeightLoadError):
+        check_weights(model_weight_specs(config.model_spec()), DictSource(extra))
+    shaped = config.with_tensor_shapes(lambda name: tuple(extra[name].shape) if name in extra else None)
+    assert {name for name, _ in shaped.unused_tensors} == {"l2.mix.vmix", "l2.norm2", "l2.norm2.b", "l2.norm2.alpha"}
+    check_weights(model_weight_specs(shaped.model_spec()), DictSource(extra))
+    # without them in the file nothing is expected
+    plain_shapes = config.with_tensor_shapes(lambda name: tuple(tensors[name].shape) if name in tensors else None)
+    assert plain_shapes.unused_tensors == ()
+    check_weights(model_weight_specs(plain_shapes.model_spec()), DictSource(tensors))
